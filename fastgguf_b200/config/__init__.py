@@ -3,5 +3,6 @@ from .base import ConfigError, ModelConfig, architecture_name, read_config_json
 from .llama import LlamaConfig
 from .zirivik import ZirivikConfig
 from .salulorn import SalulornConfig
+from .pirozen import PirozenConfig
 
-__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "ZirivikConfig", "SalulornConfig", "architecture_name", "read_config_json"]
+__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "ZirivikConfig", "SalulornConfig", "PirozenConfig", "architecture_name", "read_config_json"]

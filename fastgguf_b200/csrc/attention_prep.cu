@@ -23,7 +23,8 @@ qkv_prepare_kernel(const float *__restrict__ proj, int ld, const float *__restri
                    const float *__restrict__ cos_t, const float *__restrict__ sin_t, int tbl_half, int rot_dims,
                    const int *__restrict__ positions, const int *__restrict__ row_seq, const int *__restrict__ cu_rows,
                    const int *__restrict__ slots, const int *__restrict__ block_table, int table_width, T *__restrict__ q_out, int ldq,
-                   T *__restrict__ k_pool, T *__restrict__ v_pool, int H, int KV, int hd, int hdv, int page_size) {
+                   T *__restrict__ k_pool, T *__restrict__ v_pool, int H, int KV, int hd, int hdv, int page_size, int norm_per_head,
+                   int rot_halves) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
     pdl_launch_dependents();
@@ -51,7 +52,21 @@ qkv_prepare_kernel(const float *__restrict__ proj, int ld, const float *__restri
         for (int c = tid; c < C; c += nthr) row[c] = mine[c] + (bias ? bias[c] : 0.f);
     }
     __syncthreads();
-    if (qn_w) {
+    if (qn_w && norm_per_head) {
+        // every head of q and of k by itself: x / sqrt(mean(x^2) + eps) * w with ONE weight vector [hd] for all heads of q and
+        // one for all heads of k; a warp takes a head, its lanes the head's numbers, the sum by a shuffle tree
+        const int warp = tid >> 5, lane = tid & 31, n_warps = nthr >> 5;
+        for (int head = warp; head < H + KV; head += n_warps) {
+            float *p = row + (size_t)head * hd;
+            const float *w = head < H ? qn_w : kn_w;
+            float ss = 0.f;
+            for (int d = lane; d < hd; d += 32) ss = fmaf(p[d], p[d], ss);
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+            for (int d = lane; d < hd; d += 32) p[d] = p[d] * inv * w[d];
+        }
+        __syncthreads();
+    } else if (qn_w) {
         float sq = 0.f, sk = 0.f;
         for (int c = tid; c < Cq; c += nthr) sq = fmaf(row[c], row[c], sq);
         for (int c = tid; c < Ck; c += nthr) sk = fmaf(row[Cq + c], row[Cq + c], sk);
@@ -67,10 +82,12 @@ qkv_prepare_kernel(const float *__restrict__ proj, int ld, const float *__restri
         const float *cs = cos_t + (size_t)pos * tbl_half, *sn = sin_t + (size_t)pos * tbl_half;
         for (int e = tid; e < (H + KV) * rh; e += nthr) {
             const int head = e / rh, i = e - head * rh;
-            float *p = row + (size_t)head * hd + 2 * i;   // q heads and k heads lie one after another, all of size hd
-            const float a = p[0], b = p[1], c = cs[i], s = sn[i];
+            // q heads and k heads lie one after another, all of size hd; a pair is (2i, 2i + 1), or (i, i + rot_dims / 2)
+            float *p = row + (size_t)head * hd + (rot_halves ? i : 2 * i);
+            const int other = rot_halves ? rh : 1;
+            const float a = p[0], b = p[other], c = cs[i], s = sn[i];
             p[0] = a * c - b * s;
-            p[1] = b * c + a * s;
+            p[other] = b * c + a * s;
         }
         __syncthreads();
     }
@@ -289,11 +306,13 @@ head_gemv_kernel(const void *__restrict__ A, int a_dtype, int lda, int a_stride,
     }
 }
 
-extern "C" int fg_qkv_prepare(const float *proj, int ld, const float *bias, const float *conv_w, int taps, const float *conv_state,
-                              const float *qn_w, const float *kn_w, float eps, const float *cos_t, const float *sin_t, int tbl_half,
-                              int rot_dims, const int *positions, const int *row_seq, const int *cu_rows, const int *slots,
-                              const int *block_table, int table_width, void *q_out, int ldq, void *k_pool, void *v_pool, int dtype, int M,
-                              int H, int KV, int hd, int hdv, int page_size, cudaStream_t stream) {
+// norm_per_head: the norm weights are [hd] and every head of q and of k is normalised by itself (else: [H * hd] / [KV * hd], the
+// whole of q and of k at once); rot_halves: a rotated pair is (i, i + rot_dims / 2) of a head (else (2i, 2i + 1))
+extern "C" int fg_qkv_prepare_ext(const float *proj, int ld, const float *bias, const float *conv_w, int taps, const float *conv_state,
+                                  const float *qn_w, const float *kn_w, float eps, const float *cos_t, const float *sin_t, int tbl_half,
+                                  int rot_dims, const int *positions, const int *row_seq, const int *cu_rows, const int *slots,
+                                  const int *block_table, int table_width, void *q_out, int ldq, void *k_pool, void *v_pool, int dtype, int M,
+                                  int H, int KV, int hd, int hdv, int page_size, int norm_per_head, int rot_halves, cudaStream_t stream) {
     if (M <= 0) return 0;
     if (H <= 0 || KV <= 0 || hd <= 0 || hdv <= 0 || rot_dims < 0 || rot_dims % 2 || rot_dims > hd || rot_dims / 2 > tbl_half) return FG_ERR_BAD_SIZE;
     if (conv_w && (taps < 1 || (taps > 1 && !conv_state))) return FG_ERR_BAD_SIZE;
@@ -312,11 +331,47 @@ extern "C" int fg_qkv_prepare(const float *proj, int ld, const float *bias, cons
     if (dtype == FG_F32)
         return fg_launch(qkv_prepare_kernel<float>, dim3(M), dim3(threads), smem, stream, proj, ld, bias, conv_w, taps, conv_state, qn_w, kn_w,
                          eps, cos_t, sin_t, tbl_half, rot_dims, positions, row_seq, cu_rows, slots, block_table, table_width, (float *)q_out,
-                         ldq, (float *)k_pool, (float *)v_pool, H, KV, hd, hdv, page_size);
+                         ldq, (float *)k_pool, (float *)v_pool, H, KV, hd, hdv, page_size, norm_per_head, rot_halves);
     if (dtype == FG_BF16)
         return fg_launch(qkv_prepare_kernel<bf16>, dim3(M), dim3(threads), smem, stream, proj, ld, bias, conv_w, taps, conv_state, qn_w, kn_w,
                          eps, cos_t, sin_t, tbl_half, rot_dims, positions, row_seq, cu_rows, slots, block_table, table_width, (bf16 *)q_out, ldq,
-                         (bf16 *)k_pool, (bf16 *)v_pool, H, KV, hd, hdv, page_size);
+                         (bf16 *)k_pool, (bf16 *)v_pool, H, KV, hd, hdv, page_size, norm_per_head, rot_halves);
+    return FG_ERR_BAD_DTYPE;
+}
+
+extern "C" int fg_qkv_prepare(const float *proj, int ld, const float *bias, const float *conv_w, int taps, const float *conv_state,
+                              const float *qn_w, const float *kn_w, float eps, const float *cos_t, const float *sin_t, int tbl_half,
+                              int rot_dims, const int *positions, const int *row_seq, const int *cu_rows, const int *slots,
+                              const int *block_table, int table_width, void *q_out, int ldq, void *k_pool, void *v_pool, int dtype, int M,
+                              int H, int KV, int hd, int hdv, int page_size, cudaStream_t stream) {
+    return fg_qkv_prepare_ext(proj, ld, bias, conv_w, taps, conv_state, qn_w, kn_w, eps, cos_t, sin_t, tbl_half, rot_dims, positions, row_seq,
+                              cu_rows, slots, block_table, table_width, q_out, ldq, k_pool, v_pool, dtype, M, H, KV, hd, hdv, page_size, 0, 0, stream);
+}
+
+// ------------------------------------------------------------------ a gate per head on the heads' outputs
+// x[m, h * DV + j] *= sigmoid(gate[m, h]) in place (gate float32, one number a head and row; null: no gate), and `pad` columns
+// behind the heads are set to (1, 0, 0, ...): with the output projection's bias stored as column H * DV of its matrix, the
+// projection adds the bias in the same pass.
+template <typename T>
+__global__ void head_gate_kernel(T *__restrict__ x, int ldx, const float *__restrict__ gate, int ldg, int H, int DV, int pad) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int m = blockIdx.x;
+    T *row = x + (size_t)m * ldx;
+    if (gate)
+        for (int e = threadIdx.x; e < H * DV; e += blockDim.x) {
+            const float g = 1.0f / (1.0f + expf(-gate[(size_t)m * ldg + e / DV]));
+            row[e] = from_f32<T>(to_f32<T>(row[e]) * g);
+        }
+    for (int e = threadIdx.x; e < pad; e += blockDim.x) row[H * DV + e] = from_f32<T>(e == 0 ? 1.0f : 0.0f);
+}
+
+extern "C" int fg_head_gate(void *x, int ldx, int dtype, const float *gate, int ldg, int M, int H, int DV, int pad, cudaStream_t stream) {
+    if (M <= 0 || (!gate && pad <= 0)) return 0;
+    if (H * DV + pad > ldx) return FG_ERR_BAD_SIZE;
+    const int threads = H * DV >= 1024 ? 256 : 128;
+    if (dtype == FG_F32) return fg_launch(head_gate_kernel<float>, dim3(M), dim3(threads), 0, stream, (float *)x, ldx, gate, ldg, H, DV, pad);
+    if (dtype == FG_BF16) return fg_launch(head_gate_kernel<bf16>, dim3(M), dim3(threads), 0, stream, (bf16 *)x, ldx, gate, ldg, H, DV, pad);
     return FG_ERR_BAD_DTYPE;
 }
 

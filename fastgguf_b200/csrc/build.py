@@ -36,7 +36,7 @@ MODULES = {
     "mix": ["retention.cu", "experts.cu", "gla.cu", "attention_prep.cu", "attention_latent.cu"],
     # the C++ host: configuration, weights, cache, step function, generation loop, C interface; it opens the
     # kernel libraries above by name when a model first needs them
-    "engine": ["host/api.cpp", "host/cache.cpp", "host/config.cpp", "host/config_zirivik.cpp", "host/config_salulorn.cpp", "host/device.cpp", "host/model.cpp", "host/parts.cpp",
+    "engine": ["host/api.cpp", "host/cache.cpp", "host/config.cpp", "host/config_zirivik.cpp", "host/config_salulorn.cpp", "host/config_pirozen.cpp", "host/device.cpp", "host/model.cpp", "host/parts.cpp",
                "host/parts_recurrent.cpp", "host/parts_attention.cpp", "host/parts_experts.cpp", "host/runner.cpp", "host/safetensors.cpp", "host/host_kernels.cu"],
 }
 LINK_FLAGS = {"engine": ["-ldl"]}

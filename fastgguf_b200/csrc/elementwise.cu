@@ -484,3 +484,100 @@ extern "C" int fg_concat2(const float *a, int lda, const float *b, int ldb, void
     if (out_dtype == FG_BF16) return fg_launch(concat2_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, a, lda, b, ldb, (bf16 *)out, ldo, total, E);
     return FG_ERR_BAD_DTYPE;
 }
+
+// ------------------------------------------------------------------ two norms of the same rows
+// Blocks whose two sublayers each normalise the SAME stream with a weight of their own: out_a = x / rms(x) * w_a and
+// out_b = x / rms(x) * w_b (one statistic when the eps agree, which is the case the kernel is for; two otherwise), one pass
+// over the row.  Statistics are 32-bit; one block a row, fixed reduction order.
+template <typename TO>
+__global__ void rmsnorm_pair_kernel(const float *__restrict__ x, const float *__restrict__ w_a, const float *__restrict__ w_b,
+                                    TO *__restrict__ out_a, TO *__restrict__ out_b, int E, float eps_a, float eps_b) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float *xi = x + (size_t)blockIdx.x * E;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) { float v = xi[i]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float inv_a = 1.0f / sqrtf(ss / (float)E + eps_a), inv_b = 1.0f / sqrtf(ss / (float)E + eps_b);
+    TO *oa = out_a + (size_t)blockIdx.x * E, *ob = out_b + (size_t)blockIdx.x * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        const float v = xi[i];
+        oa[i] = from_f32<TO>(v * inv_a * w_a[i]);
+        ob[i] = from_f32<TO>(v * inv_b * w_b[i]);
+    }
+}
+
+extern "C" int fg_rmsnorm_pair(const float *x, const float *w_a, const float *w_b, void *out_a, void *out_b, int out_dtype, int R, int E,
+                               float eps_a, float eps_b, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    const int threads = E >= 4096 ? 512 : (E >= 1024 ? 256 : (E >= 256 ? 128 : 64));
+    if (out_dtype == FG_F32)
+        return fg_launch(rmsnorm_pair_kernel<float>, dim3(R), dim3(threads), 0, stream, x, w_a, w_b, (float *)out_a, (float *)out_b, E, eps_a, eps_b);
+    if (out_dtype == FG_BF16)
+        return fg_launch(rmsnorm_pair_kernel<bf16>, dim3(R), dim3(threads), 0, stream, x, w_a, w_b, (bf16 *)out_a, (bf16 *)out_b, E, eps_a, eps_b);
+    return FG_ERR_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------ the stream as a contraction's input
+// out[m, c] = T(x[m, c]): the float32 stream itself (no norm) rounded to the activation dtype.
+template <typename T>
+__global__ void cast_rows_kernel(const float *__restrict__ x, int ldx, T *__restrict__ out, int ldo, size_t total, int E) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const size_t m = i / (size_t)E;
+        const int c = (int)(i - m * (size_t)E);
+        out[m * ldo + c] = from_f32<T>(x[m * ldx + c]);
+    }
+}
+
+extern "C" int fg_cast_rows(const float *x, int ldx, void *out, int out_dtype, int ldo, int M, int E, cudaStream_t stream) {
+    const size_t total = (size_t)M * (size_t)E;
+    if (total == 0) return 0;
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+    if (out_dtype == FG_F32) return fg_launch(cast_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, ldx, (float *)out, ldo, total, E);
+    if (out_dtype == FG_BF16) return fg_launch(cast_rows_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, ldx, (bf16 *)out, ldo, total, E);
+    return FG_ERR_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------ gelu(z) * (a slice of a token's row of a table)
+// out[m, j] = gelu_tanh(z[m, j]) * table[tokens[m], col0 + j], j < D, with
+// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).  z is float32; the product is formed in float32.
+__device__ __forceinline__ float gelu_tanh_f32(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename TT, typename TO>
+__global__ void gelu_mul_gather_kernel(const float *__restrict__ z, int ldz, const TT *__restrict__ table, int ldt, int col0,
+                                       const int *__restrict__ tokens, TO *__restrict__ out, int ldo, size_t total, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const size_t m = i / (size_t)D;
+        const int j = (int)(i - m * (size_t)D);
+        const float e = to_f32<TT>(table[(size_t)tokens[m] * ldt + col0 + j]);
+        out[m * ldo + j] = from_f32<TO>(gelu_tanh_f32(z[m * ldz + j]) * e);
+    }
+}
+
+extern "C" int fg_gelu_mul_gather(const float *z, int ldz, const void *table, int table_dtype, int ldt, int col0, const int *tokens,
+                                  void *out, int out_dtype, int ldo, int M, int D, cudaStream_t stream) {
+    const size_t total = (size_t)M * (size_t)D;
+    if (total == 0) return 0;
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+#define GMG_LAUNCH(TT, TO) fg_launch(gelu_mul_gather_kernel<TT, TO>, dim3(blocks), dim3(256), 0, stream, z, ldz, (const TT *)table, ldt, col0, tokens, \
+                                     (TO *)out, ldo, total, D)
+    if (table_dtype == FG_F32 && out_dtype == FG_F32) return GMG_LAUNCH(float, float);
+    if (table_dtype == FG_BF16 && out_dtype == FG_BF16) return GMG_LAUNCH(bf16, bf16);
+    if (table_dtype == FG_F32 && out_dtype == FG_BF16) return GMG_LAUNCH(float, bf16);
+    if (table_dtype == FG_BF16 && out_dtype == FG_F32) return GMG_LAUNCH(bf16, float);
+#undef GMG_LAUNCH
+    return FG_ERR_BAD_DTYPE;
+}

@@ -135,7 +135,95 @@ extern "C" int fg_moe_route(const float *logits, int M, int X, int top, int *pai
                      slot_of);
 }
 
+// ------------------------------------------------------------------ routing, kind 1: softmax scores, a selection bias, groups
+// scores s = softmax(z) over all X router outputs; the choice is made on c = s + bias (bias: a float per output), the
+// weights from s.  The outputs form n_groups equal runs of neighbours; a group's score is its largest c, and only outputs of
+// the `keep` best groups can be chosen (the others count as minus infinity, whatever sign c has).  The `top` outputs with the
+// largest c are taken (ties to the lower index); their weights are s / (sum of the chosen s + 1e-20) * scale.  Outputs at and
+// beyond n_real have no expert behind them (the caller gives them a meaning, e.g. "the input itself"); they are routed,
+// grouped and counted like the others.  One block; a thread a row.  logits: [M, X] float32.
+__global__ void __launch_bounds__(1024)
+moe_route_grouped_kernel(const float *__restrict__ logits, const float *__restrict__ bias, int M, int X, int top, int n_groups, int keep,
+                         float scale, int *__restrict__ pair_expert, float *__restrict__ pair_weight, int *__restrict__ offsets,
+                         int *__restrict__ order, int *__restrict__ slot_of) {
+    __shared__ int counts[MOE_MAX_EXPERTS], cursor[MOE_MAX_EXPERTS];
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int e = threadIdx.x; e < X; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    const int per = X / n_groups;
+    for (int r = threadIdx.x; r < M; r += blockDim.x) {
+        const float *z = logits + (size_t)r * X;
+        float zmax = z[0];
+        for (int e = 1; e < X; e++) zmax = fmaxf(zmax, z[e]);
+        float sum = 0.f;
+        for (int e = 0; e < X; e++) sum += expf(z[e] - zmax);
+        const float inv = 1.0f / sum;
+        // the groups that stay: `keep` times the best group not yet taken
+        unsigned long long allowed = 0ull;
+        for (int k = 0; k < keep; k++) {
+            int best = -1;
+            float bs = 0.f;
+            for (int g = 0; g < n_groups; g++) {
+                if (allowed >> g & 1ull) continue;
+                float gs = -INFINITY;
+                for (int e = g * per; e < (g + 1) * per; e++) gs = fmaxf(gs, expf(z[e] - zmax) * inv + (bias ? bias[e] : 0.f));
+                if (best < 0 || gs > bs) { best = g; bs = gs; }
+            }
+            allowed |= 1ull << best;
+        }
+        int chosen[MOE_MAX_TOP];
+        float s_of[MOE_MAX_TOP], total = 0.f;
+        for (int k = 0; k < top; k++) {
+            int best = -1;
+            float bc = 0.f, bsc = 0.f;
+            for (int e = 0; e < X; e++) {
+                if (!(allowed >> (e / per) & 1ull)) continue;
+                bool taken = false;
+                for (int q = 0; q < k; q++) taken = taken || chosen[q] == e;
+                if (taken) continue;
+                const float sc = expf(z[e] - zmax) * inv, c = sc + (bias ? bias[e] : 0.f);
+                if (best < 0 || c > bc) { best = e; bc = c; bsc = sc; }
+            }
+            chosen[k] = best;
+            s_of[k] = bsc;
+            total += bsc;
+        }
+        const float norm = scale / (total + 1e-20f);
+        for (int k = 0; k < top; k++) {
+            pair_expert[(size_t)r * top + k] = chosen[k];
+            pair_weight[(size_t)r * top + k] = s_of[k] * norm;
+            atomicAdd(&counts[chosen[k]], 1);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < X; e++) { offsets[e] = at; cursor[e] = at; at += counts[e]; }
+        offsets[X] = at;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < M * top; p += blockDim.x) {
+        int slot = atomicAdd(&cursor[pair_expert[p]], 1);
+        order[slot] = p;
+        slot_of[p] = slot;
+    }
+}
+
+extern "C" int fg_moe_route_grouped(const float *logits, const float *bias, int M, int X, int top, int n_groups, int keep, float scale,
+                                    int *pair_expert, float *pair_weight, int *offsets, int *order, int *slot_of, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (X <= 0 || X > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP || n_groups <= 0 || n_groups > 64 || X % n_groups || keep <= 0 ||
+        keep > n_groups || top > keep * (X / n_groups))
+        return FG_ERR_BAD_SIZE;
+    int threads = M >= 1024 ? 1024 : ((M + 31) / 32) * 32;
+    return fg_launch(moe_route_grouped_kernel, dim3(1), dim3(threads), 0, stream, logits, bias, M, X, top, n_groups, keep, scale, pair_expert,
+                     pair_weight, offsets, order, slot_of);
+}
+
+// limit > 0: the clamped form above; limit <= 0: the plain gated form silu(g) * u, silu(z) = z * sigmoid(z)
 __device__ __forceinline__ float expert_act(float g, float u, float limit, float alpha) {
+    if (!(limit > 0.f)) return g / (1.0f + expf(-g)) * u;
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
@@ -204,7 +292,7 @@ moe_tile_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void 
     for (int i = 0; i < 4; i++) {
         const int slot = s0 + ty + 16 * i;
         if (slot >= s1) continue;
-        const float w = FIRST ? pair_weight[order[slot]] : 1.0f;
+        const float w = (FIRST && pair_weight) ? pair_weight[order[slot]] : 1.0f;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx + 16 * j;
@@ -224,17 +312,18 @@ template <typename T, bool FIRST>
 __global__ void __launch_bounds__(256)
 moe_rows_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void *__restrict__ out, int ldo,
                 const int *__restrict__ pair_expert, const int *__restrict__ order, const float *__restrict__ pair_weight, int top,
-                int N, int K, float limit, float alpha) {
+                int X, int N, int K, float limit, float alpha) {
     extern __shared__ __align__(16) float xs[];      // [K] the slot's input row
     pdl_launch_dependents();
     pdl_wait();
     const int slot = blockIdx.y, pair = order[slot], e = pair_expert[pair];
+    if (e >= X) return;                              // a choice without an expert behind it (the caller handles it)
     const T *a = A + (size_t)(FIRST ? pair / top : slot) * lda;
     for (int k = threadIdx.x; k < K; k += 256) xs[k] = to_f32<T>(a[k]);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const T *We = W + (size_t)e * (FIRST ? 2 : 1) * N * K;
-    const float w = FIRST ? pair_weight[pair] : 1.0f;
+    const float w = (FIRST && pair_weight) ? pair_weight[pair] : 1.0f;
     constexpr int VEC = 16 / (int)sizeof(T);         // elements a 16-byte load brings
     const bool vec = (K % VEC) == 0 && (((uintptr_t)W) & 15) == 0;
     constexpr int MR_ROWS = MR_ROWS_OF(FIRST);
@@ -383,7 +472,7 @@ moe_rows_grouped_kernel(const T *__restrict__ A, int lda, const T *__restrict__ 
         __syncthreads();
         float w[MG_SLOTS];
 #pragma unroll
-        for (int i = 0; i < MG_SLOTS; i++) w[i] = (FIRST && i < cnt) ? pair_weight[order[s0 + i]] : 1.0f;
+        for (int i = 0; i < MG_SLOTS; i++) w[i] = (FIRST && pair_weight && i < cnt) ? pair_weight[order[s0 + i]] : 1.0f;
         if (n0 >= N) continue;
         switch (cnt) {
         case 1: moe_group_rows<T, FIRST, 1>(We, xs, out, ldo, s0, w, N, K, limit, alpha, n0, lane); break;
@@ -427,9 +516,9 @@ extern "C" int fg_moe_first(const void *x, int ldx, const void *w_in, void *y, i
         dim3 grid((F + 8 * MR_ROWS_OF(true) - 1) / (8 * MR_ROWS_OF(true)), P);
         if (dtype == FG_F32)
             return fg_launch(moe_rows_kernel<float, true>, grid, dim3(256), (size_t)E * 4, stream, (const float *)x, ldx, (const float *)w_in,
-                             y, ldy, pair_expert, order, pair_weight, top, F, E, limit, alpha);
+                             y, ldy, pair_expert, order, pair_weight, top, X, F, E, limit, alpha);
         return fg_launch(moe_rows_kernel<bf16, true>, grid, dim3(256), (size_t)E * 4, stream, (const bf16 *)x, ldx, (const bf16 *)w_in, y, ldy,
-                         pair_expert, order, pair_weight, top, F, E, limit, alpha);
+                         pair_expert, order, pair_weight, top, X, F, E, limit, alpha);
     }
     dim3 grid((F + MT - 1) / MT, (P + MT - 1) / MT + X);
     if (grid.y > 65535) return FG_ERR_BAD_SIZE;
@@ -454,9 +543,9 @@ extern "C" int fg_moe_second(const void *y, int ldy, const void *w_out, float *o
         dim3 grid((E + 8 * MR_ROWS_OF(false) - 1) / (8 * MR_ROWS_OF(false)), P);
         if (dtype == FG_F32)
             return fg_launch(moe_rows_kernel<float, false>, grid, dim3(256), (size_t)F * 4, stream, (const float *)y, ldy, (const float *)w_out,
-                             (void *)out, ldo, pair_expert, order, (const float *)nullptr, top, E, F, 0.f, 0.f);
+                             (void *)out, ldo, pair_expert, order, (const float *)nullptr, top, X, E, F, 0.f, 0.f);
         return fg_launch(moe_rows_kernel<bf16, false>, grid, dim3(256), (size_t)F * 4, stream, (const bf16 *)y, ldy, (const bf16 *)w_out,
-                         (void *)out, ldo, pair_expert, order, (const float *)nullptr, top, E, F, 0.f, 0.f);
+                         (void *)out, ldo, pair_expert, order, (const float *)nullptr, top, X, E, F, 0.f, 0.f);
     }
     dim3 grid((E + MT - 1) / MT, (P + MT - 1) / MT + X);
     if (grid.y > 65535) return FG_ERR_BAD_SIZE;
@@ -498,7 +587,7 @@ __global__ void moe_act_kernel(const float *__restrict__ gu, const int *__restri
     pdl_launch_dependents();
     pdl_wait();
     const int slot = blockIdx.x;
-    const float w = pair_weight[order[slot]];
+    const float w = pair_weight ? pair_weight[order[slot]] : 1.0f;
     const float *g = gu + (size_t)slot * 2 * F, *u = g + F;
     for (int i = threadIdx.x; i < F; i += blockDim.x) y[(size_t)slot * F + i] = from_f32<T>(expert_act(w * g[i], w * u[i], limit, alpha));
 }
@@ -529,4 +618,40 @@ extern "C" int fg_moe_combine(const float *slot_out, int ld, const int *slot_of,
                               cudaStream_t stream) {
     if (M <= 0) return 0;
     return fg_launch(moe_combine_kernel, dim3(M), dim3(E >= 1024 ? 256 : 128), 0, stream, slot_out, ld, slot_of, t, top, E, accumulate);
+}
+
+// ------------------------------------------------------------------ weighted sum of a row's experts, in the order of its choices
+// t[r] (+)= sum_k w[r, k] * (expert[r, k] < n_real ? slot_out[slot_of[r, k]] : x[r]): the routing weight multiplies the expert's
+// OUTPUT, and a choice at or beyond n_real stands for the row's own input x (an "identity expert").
+template <typename T>
+__global__ void moe_combine_weighted_kernel(const float *__restrict__ slot_out, int ld, const int *__restrict__ slot_of,
+                                            const int *__restrict__ pair_expert, const float *__restrict__ pair_weight,
+                                            const T *__restrict__ x, int ldx, int n_real, float *__restrict__ t, int top, int E, int accumulate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top; k++) {
+            const int p = r * top + k;
+            const float v = pair_expert[p] < n_real ? slot_out[(size_t)slot_of[p] * ld + i] : to_f32<T>(x[(size_t)r * ldx + i]);
+            s = fmaf(pair_weight[p], v, s);
+        }
+        if (accumulate) t[(size_t)r * E + i] += s;
+        else t[(size_t)r * E + i] = s;
+    }
+}
+
+extern "C" int fg_moe_combine_weighted(const float *slot_out, int ld, const int *slot_of, const int *pair_expert, const float *pair_weight,
+                                       const void *x, int ldx, int dtype, int n_real, float *t, int M, int top, int E, int accumulate,
+                                       cudaStream_t stream) {
+    if (M <= 0) return 0;
+    const int threads = E >= 1024 ? 256 : 128;
+    if (dtype == FG_F32)
+        return fg_launch(moe_combine_weighted_kernel<float>, dim3(M), dim3(threads), 0, stream, slot_out, ld, slot_of, pair_expert, pair_weight,
+                         (const float *)x, ldx, n_real, t, top, E, accumulate);
+    if (dtype == FG_BF16)
+        return fg_launch(moe_combine_weighted_kernel<bf16>, dim3(M), dim3(threads), 0, stream, slot_out, ld, slot_of, pair_expert, pair_weight,
+                         (const bf16 *)x, ldx, n_real, t, top, E, accumulate);
+    return FG_ERR_BAD_DTYPE;
 }

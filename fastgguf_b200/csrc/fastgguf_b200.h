@@ -43,6 +43,14 @@ int fg_softcap(float *logits, int R, int V, int ld, float cap, cudaStream_t stre
 int fg_concat2(const float *a, int lda, const float *b, int ldb, void *out, int out_dtype, int ldo, int M, int E,
                cudaStream_t stream);
 int fg_silu_mul(const void *gu, void *out, int dtype, int M, int F, cudaStream_t stream);
+/* out_a = x / rms(x) * w_a and out_b = x / rms(x) * w_b of the same float32 rows, one pass */
+int fg_rmsnorm_pair(const float *x, const float *w_a, const float *w_b, void *out_a, void *out_b, int out_dtype, int R, int E,
+                    float eps_a, float eps_b, cudaStream_t stream);
+/* the float32 rows themselves in another dtype */
+int fg_cast_rows(const float *x, int ldx, void *out, int out_dtype, int ldo, int M, int E, cudaStream_t stream);
+/* out[m, j] = gelu_tanh(z[m, j]) * table[tokens[m], col0 + j], j < D */
+int fg_gelu_mul_gather(const float *z, int ldz, const void *table, int table_dtype, int ldt, int col0, const int *tokens, void *out,
+                       int out_dtype, int ldo, int M, int D, cudaStream_t stream);
 int fg_decode_advance(int *tokens, int *positions, const int *next_tokens, const int *active, int B, cudaStream_t stream);
 int fg_gemm_generic(const void *A, int a_dtype, int lda, const void *W, int w_dtype, int ldw, void *C, int out_dtype,
                     int ldc, int accumulate, int M, int N, int K, cudaStream_t stream);
@@ -95,6 +103,15 @@ int fg_qkv_prepare(const float *proj, int ld, const float *bias, const float *co
                    int rot_dims, const int *positions, const int *row_seq, const int *cu_rows, const int *slots,
                    const int *block_table, int table_width, void *q_out, int ldq, void *k_pool, void *v_pool, int dtype, int M,
                    int H, int KV, int hd, int hdv, int page_size, cudaStream_t stream);
+/* the same with the norm per head (weights [hd]) instead of over the whole of q and of k, and with rotated pairs
+   (i, i + rot_dims / 2) instead of (2i, 2i + 1) */
+int fg_qkv_prepare_ext(const float *proj, int ld, const float *bias, const float *conv_w, int taps, const float *conv_state,
+                       const float *qn_w, const float *kn_w, float eps, const float *cos_t, const float *sin_t, int tbl_half,
+                       int rot_dims, const int *positions, const int *row_seq, const int *cu_rows, const int *slots,
+                       const int *block_table, int table_width, void *q_out, int ldq, void *k_pool, void *v_pool, int dtype, int M,
+                       int H, int KV, int hd, int hdv, int page_size, int norm_per_head, int rot_halves, cudaStream_t stream);
+/* x[m, h * DV + j] *= sigmoid(gate[m, h]) in place (gate null: none); `pad` columns behind the heads become (1, 0, 0, ...) */
+int fg_head_gate(void *x, int ldx, int dtype, const float *gate, int ldg, int M, int H, int DV, int pad, cudaStream_t stream);
 int fg_conv_state_update(const float *proj, int ld, const float *bias, int taps, float *conv_state, const int *cu_rows,
                          const int *slots, int n_seq, int C, cudaStream_t stream);
 int fg_latent_append(const float *kv, int ld, const float *norm_w, float eps, const float *cos_t, const float *sin_t, int tbl_half,
@@ -129,6 +146,10 @@ int fg_moe_act(const float *gu, const int *order, const float *pair_weight, void
                float alpha, cudaStream_t stream);
 int fg_moe_route(const float *logits, int M, int X, int top, int *pair_expert, float *pair_weight, int *offsets, int *order,
                  int *slot_of, cudaStream_t stream);
+/* softmax scores, choice on score + bias among the `keep` best of n_groups groups, weights = chosen scores / their sum * scale */
+int fg_moe_route_grouped(const float *logits, const float *bias, int M, int X, int top, int n_groups, int keep, float scale,
+                         int *pair_expert, float *pair_weight, int *offsets, int *order, int *slot_of, cudaStream_t stream);
+/* pair_weight null: the inputs are not weighted; limit <= 0: the activation is silu(gate) * up */
 int fg_moe_first(const void *x, int ldx, const void *w_in, void *y, int ldy, int dtype, const int *pair_expert,
                  const int *offsets, const int *order, const float *pair_weight, int M, int X, int top, int F, int E,
                  float limit, float alpha, cudaStream_t stream);
@@ -136,6 +157,10 @@ int fg_moe_second(const void *y, int ldy, const void *w_out, float *out, int ldo
                   const int *offsets, const int *order, int M, int X, int top, int F, int E, cudaStream_t stream);
 int fg_moe_combine(const float *slot_out, int ld, const int *slot_of, float *t, int M, int top, int E, int accumulate,
                    cudaStream_t stream);
+/* t[r] (+)= sum_k w[r, k] * (expert[r, k] < n_real ? slot_out[slot_of[r, k]] : x[r]) */
+int fg_moe_combine_weighted(const float *slot_out, int ld, const int *slot_of, const int *pair_expert, const float *pair_weight,
+                            const void *x, int ldx, int dtype, int n_real, float *t, int M, int top, int E, int accumulate,
+                            cudaStream_t stream);
 
 /* ---- libfg_tc: bf16 contraction on tcgen05 / TMA / tensor memory
  * epi: 0 bf16 out, 1 f32 out, 2 f32 out += (residual add), 3 silu(gate) * up on interleaved rows, 4 bf16 out of max(x, 0)^2 */

@@ -13,7 +13,10 @@
  *                  "feed_forward_norm": PART}, ...],            "feed_forward": null: a layer without one (then
  *                                                               no feed_forward_norm either); optional
  *                                                               "mixer_post_norm", "feed_forward_post_norm": PART;
- *                                                               block "parallel" has no feed_forward_norm
+ *                                                               block "parallel" has no feed_forward_norm, or one
+ *                                                               (then each sublayer reads a norm of its own);
+ *                                                               optional "token_input": PART, role token_input:
+ *                                                               x <- x + f(x, the rows' tokens) behind the sublayers
  *    "schedule": [{"layer": 0, "cache_from": null}, ...],      the order in which layers run: an entry may
  *                                                               name a layer twice (a cache of its own each
  *                                                               time) or read an EARLIER entry's cache;
@@ -56,7 +59,11 @@
  *                                   tensors router.weight, experts.<e>.gate/up/down_proj.weight
  *   block         "prenorm"        x += mixer(norm1(x)); x += feed_forward(norm2(x))
  *                 "sandwich"       x += post1(mixer(norm1(x))); x += post2(feed_forward(norm2(x)))
- *                 "parallel"       x += mixer(norm1(x)) + feed_forward(norm1(x))
+ *                 "parallel"       x += mixer(norm1(x)) + feed_forward(norm1(x)), or, with a feed_forward_norm,
+ *                                  x += mixer(norm1(x)) + feed_forward(norm2(x)), both norms of the same x
+ *   token_input   "gated_token_embedding"  {hidden_size, vocab_size, dim, table_dim, column, eps}   e = table[token, column ..
+ *                                   column + dim), y = W_proj (gelu_tanh(W_gate x) * e), x <- x + y / rms(y) * w; tensors table
+ *                                   [vocab, table_dim] (layers may share it), gate [dim, E], proj [E, dim], norm [E]
  *   stream_map    "concat_linear"  {hidden_size}   x <- W [x; embedding output], W [E, 2 E]; tensor weight
  *   embedding     "embedding"      {vocab_size, hidden_size, scale: 1.0}
  *   head          "lm_head"        {vocab_size, hidden_size, softcap: null}   logits <- cap tanh(logits / cap)
@@ -86,6 +93,7 @@ extern "C" {
 #define FG_ROLE_EMBEDDING 5
 #define FG_ROLE_HEAD 6
 #define FG_ROLE_STREAM_MAP 7   /* built-in kinds only: a map of the residual stream that also reads the embedding's output */
+#define FG_ROLE_TOKEN_INPUT 8  /* built-in kinds only: what a layer adds to the stream from its tokens, behind its sublayers */
 
 typedef struct fg_tensor_decl {
     char name[96];           /* the part's local tensor name */

@@ -921,6 +921,7 @@ static std::map<std::string, ExpectedTensor> declared_tensors(const ModelSpec &s
         }
         if (!l.mixer_post_norm.kind.empty()) build(FG_ROLE_NORM, l.mixer_post_norm);
         if (!l.feed_forward_post_norm.kind.empty()) build(FG_ROLE_NORM, l.feed_forward_post_norm);
+        if (!l.token_input.kind.empty()) build(FG_ROLE_TOKEN_INPUT, l.token_input);
     }
     if (!spec.reentry.kind.empty()) build(FG_ROLE_STREAM_MAP, spec.reentry);
     build(FG_ROLE_NORM, spec.final_norm);

@@ -156,9 +156,10 @@ Json merge_generation_config(const std::string &model_dir, const Json &d) {
 static std::mutex g_registry_mutex;
 std::unique_ptr<ModelConfig> zirivik_config_from_json(const Json &d);        // config_zirivik.cpp
 std::unique_ptr<ModelConfig> salulorn_config_from_json(const Json &d);       // config_salulorn.cpp
+std::unique_ptr<ModelConfig> pirozen_config_from_json(const Json &d);        // config_pirozen.cpp
 static std::map<std::string, ConfigReader> &registry() {
     static std::map<std::string, ConfigReader> r = {{"LlamaForCausalLM", &LlamaConfig::from_json}, {"Zirivik", &zirivik_config_from_json},
-                                                    {"Salulorn", &salulorn_config_from_json}};
+                                                    {"Salulorn", &salulorn_config_from_json}, {"Pirozen", &pirozen_config_from_json}};
     return r;
 }
 

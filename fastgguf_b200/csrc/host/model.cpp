@@ -51,6 +51,7 @@ ModelSpec ModelSpec::from_json(const Json &j) {
         if (!l.get("mixer_post_norm").is_null()) ls.mixer_post_norm = part_spec_from_json(l.get("mixer_post_norm"), "mixer_post_norm");
         if (!l.get("feed_forward_post_norm").is_null())
             ls.feed_forward_post_norm = part_spec_from_json(l.get("feed_forward_post_norm"), "feed_forward_post_norm");
+        if (!l.get("token_input").is_null()) ls.token_input = part_spec_from_json(l.get("token_input"), "token_input");
         s.layers.push_back(std::move(ls));
     }
     for (auto &r : j.get("schedule").items()) {
@@ -118,6 +119,10 @@ DecoderModel::DecoderModel(const ModelSpec &spec_, int dtype, int device, cudaSt
         std::unique_ptr<Block> b = build_block(layer.block, runtime);
         b->mixer = mixer; b->feed_forward = ffn; b->mixer_norm = n1; b->feed_forward_norm = n2;
         b->mixer_post_norm = p1; b->feed_forward_post_norm = p2;
+        if (!layer.token_input.kind.empty()) {
+            b->token_input = dynamic_cast<TokenInput *>(build(FG_ROLE_TOKEN_INPUT, layer.token_input));
+            if (!b->token_input) fail(FG_E_INTERNAL, "a part was registered under the wrong role");
+        }
         b->check_layer();
         blocks_.push_back(std::move(b));
         mixers_.push_back(mixer);
@@ -492,9 +497,14 @@ Tensor DecoderModel::forward(Runtime &rt, const Batch &batch) {
         // blocks that finish the next norm themselves hand it to a block of the same habit only (any dtype)
         if (block_at(i)->finished_norms()) next = (i + 1 < n && block_at(i + 1)->finished_norms()) ? block_at(i + 1)->mixer_norm : nullptr;
         else if (i + 1 < n && block_at(i + 1)->finished_norms()) next = nullptr;
-        if (reenters(i + 1)) next = nullptr;
+        // a layer that adds a token input behind its sublayers changes the stream after its last projection
+        if (reenters(i + 1) || block_at(i)->token_input) next = nullptr;
         rt.arena->begin_layer((int)i);                 // this entry's temporaries reuse the memory of entry i - 2
         pending = block_at(i)->forward(rt, x, batch, io[i], pending, next);
+        if (block_at(i)->token_input) {
+            block_at(i)->token_input->forward(rt, batch, x);
+            pending = DeferredNorm();
+        }
         rt.arena->end_layers();                        // what follows the block belongs to the step, not to the layer
     }
     rt.arena->end_layers();
@@ -529,7 +539,9 @@ void DecoderModel::block_forward(int entry, const std::vector<std::pair<int, int
     Tensor x = runtime.arena->matrix(M, spec.hidden_size, FG_F32);
     size_t bytes = (size_t)M * (size_t)spec.hidden_size * 4;
     FG_CUDA(cudaMemcpyAsync(x.data, x_host, bytes, cudaMemcpyHostToDevice, runtime.stream));
-    blocks_[(size_t)spec.schedule[(size_t)entry].layer]->forward(runtime, x, batch, io[(size_t)entry], DeferredNorm(), nullptr);
+    Block *blk = blocks_[(size_t)spec.schedule[(size_t)entry].layer].get();
+    blk->forward(runtime, x, batch, io[(size_t)entry], DeferredNorm(), nullptr);
+    if (blk->token_input) blk->token_input->forward(runtime, batch, x);
     FG_CUDA(cudaMemcpyAsync(x_host, x.data, bytes, cudaMemcpyDeviceToHost, runtime.stream));
     FG_CUDA(cudaStreamSynchronize(runtime.stream));
     cache->commit(steps);

@@ -31,6 +31,7 @@ struct LayerSpec {
     std::string block;
     PartSpec mixer, feed_forward, mixer_norm, feed_forward_norm;
     PartSpec mixer_post_norm, feed_forward_post_norm;    // optional; a part with an empty kind is absent
+    PartSpec token_input;                            // optional: what the layer adds from its tokens, behind the sublayers
     bool has_feed_forward() const { return !feed_forward.kind.empty(); }
 };
 struct RunSpec {

@@ -13,8 +13,8 @@ static const int EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL = 3;
 static const int KERNEL_BAD_SIZE = 10002;
 
 const char *role_name(int role) {
-    static const char *n[] = {"norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "stream_map"};
-    return role >= 0 && role <= 7 ? n[role] : "?";
+    static const char *n[] = {"norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "stream_map", "token_input"};
+    return role >= 0 && role <= 8 ? n[role] : "?";
 }
 
 // ------------------------------------------------------------------------------------ parameters
@@ -683,6 +683,8 @@ private:
     Linear fused_, gate_up_, down_;
 };
 
+std::unique_ptr<FeedForward> make_swiglu(const Json &params) { return std::make_unique<SwiGLU>(params); }
+
 // ------------------------------------------------------------------------------------ pre-norm block
 // x += mixer(norm1(x)); x += feed_forward(norm2(x)): the norm stands before attention (fastgguf.c:4686-4687) and
 // before the feed-forward (:4865-4866); both residual sums add the projection onto the un-normalized input
@@ -790,15 +792,18 @@ public:
 // x += mixer(norm1(x)) + feed_forward(norm1(x)): ONE norm, both sublayers read its output, and both add their results to the
 // float32 stream (the mixer first).  In bfloat16 the started norm that the block before handed over serves both sublayers,
 // and the last sublayer's output projection starts the next block's norm.
+// With a feed_forward_norm: x += mixer(norm1(x)) + feed_forward(norm2(x)), two norms of the SAME x with a weight each.  Both
+// are formed (one kernel, one statistic a row) before either sublayer adds to the stream.
 class ParallelBlock : public Block {
 public:
     void check_layer() const override {
         if (!mixer || !mixer_norm) fail(FG_E_CONFIG, "a layer needs a mixer and its norm");
-        if (feed_forward_norm || mixer_post_norm || feed_forward_post_norm)
-            fail(FG_E_CONFIG, "block 'parallel' has one norm, in front of both sublayers");
+        if (mixer_post_norm || feed_forward_post_norm) fail(FG_E_CONFIG, "block 'parallel' has its norms in front of the sublayers");
+        if (feed_forward_norm && !feed_forward) fail(FG_E_CONFIG, "a layer without a feed-forward cannot have a norm for one");
     }
     DeferredNorm forward(Runtime &rt, Tensor &x, const Batch &batch, const LayerIO &io, const DeferredNorm &pending,
                          Norm *next_norm) override {
+        if (feed_forward_norm) return forward_two_norms(rt, x, batch, io, pending, next_norm);
         const bool bf16 = rt.dtype == FG_BF16;
         const bool mixer_defers = bf16 && mixer->supports_deferred_norm();
         const bool ffn_defers = bf16 && feed_forward && feed_forward->supports_deferred_norm();
@@ -819,6 +824,85 @@ public:
         out = feed_forward->forward(rt, finished(), nullptr, batch, x, ffn_defers ? next_norm : nullptr);
         return ffn_defers ? out : DeferredNorm();
     }
+
+private:
+    DeferredNorm forward_two_norms(Runtime &rt, Tensor &x, const Batch &batch, const LayerIO &io, const DeferredNorm &pending,
+                                   Norm *next_norm) {
+        const int M = (int)x.rows, E = (int)x.cols;
+        Tensor xa, xb;
+        // a norm the block before finished for this block's mixer is taken; the feed-forward's is made here
+        if (pending.defined() && pending.tiles == 0) {
+            xa = pending.xw;
+            xb = feed_forward_norm->forward(rt, x, nullptr, 0);
+        } else if (mixer_norm->deferrable() && feed_forward_norm->deferrable() && mixer_norm->weight() && feed_forward_norm->weight() &&
+                   mixer_norm->size() == E && feed_forward_norm->size() == E) {
+            xa = rt.arena->matrix(M, E, rt.dtype);
+            xb = rt.arena->matrix(M, E, rt.dtype);
+            if (M > 0)
+                FG_LAUNCH("core", fg_rmsnorm_pair, x.ptr<float>(), mixer_norm->weight(), feed_forward_norm->weight(), xa.data, xb.data, rt.dtype, M, E,
+                          mixer_norm->eps(), feed_forward_norm->eps(), rt.stream);
+        } else {
+            xa = mixer_norm->forward(rt, x, nullptr, 0);
+            xb = feed_forward_norm->forward(rt, x, nullptr, 0);
+        }
+        const bool ffn_defers = rt.dtype == FG_BF16 && feed_forward->supports_deferred_norm();
+        mixer->forward(rt, xa, nullptr, batch, io, x, nullptr);
+        DeferredNorm out = feed_forward->forward(rt, xb, nullptr, batch, x, ffn_defers ? next_norm : nullptr);
+        return ffn_defers ? out : DeferredNorm();
+    }
+};
+
+// ------------------------------------------------------------------------------------ per-layer token input
+// A second embedding table gives every layer a few numbers a token: e = table[token, column .. column + dim).  The layer gates
+// them by the stream, projects them to the width and adds the normalised result:
+//     g = gelu_tanh(W_gate x) * e,   y = W_proj g,   x <- x + y / sqrt(mean(y^2) + eps) * w
+// x is the stream itself (no norm in front).  The residual sum and the norm's statistics are 32-bit; in bfloat16 the stream is
+// rounded for the gate contraction as every contraction's input is, and its float32 result meets gelu and e in float32.
+class GatedTokenEmbedding : public TokenInput {
+public:
+    GatedTokenEmbedding(const Json &p) {
+        const char *me = "gated_token_embedding";
+        E_ = param_int(p, "hidden_size", me);
+        V_ = param_int(p, "vocab_size", me);
+        D_ = param_int(p, "dim", me);
+        col_ = param_int(p, "column", 0, me);
+        TD_ = param_int(p, "table_dim", col_ + D_, me);
+        eps_ = (float)param_float(p, "eps", me);
+        if (E_ <= 0 || V_ <= 0 || D_ <= 0 || col_ < 0 || col_ + D_ > TD_) fail(FG_E_CONFIG, "gated_token_embedding: sizes must be positive and the columns inside the table");
+        if (!(eps_ > 0.f)) fail(FG_E_CONFIG, "gated_token_embedding: eps must be positive");
+    }
+    std::vector<TensorDecl> tensor_decls() const override {
+        return {{"table", {V_, TD_}, false, 0, 1.0f}, {"gate", {D_, E_}}, {"proj", {E_, D_}}, {"norm", {E_}, false, 1, 0.01f}};
+    }
+    void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
+        table_ = tensor_of(tensors, "table");
+        gate_ = Linear(tensor_of(tensors, "gate"));
+        proj_ = Linear(tensor_of(tensors, "proj"));
+        const Weight &w = tensor_of(tensors, "norm");
+        norm_w_ = w.t.dtype == FG_F32 ? w : concat_rows({w}, FG_F32, rt.stream);
+    }
+    void forward(Runtime &rt, const Batch &b, Tensor &x) override {
+        const int M = (int)x.rows;
+        if (M == 0) return;
+        Tensor xin = x;
+        if (rt.dtype != FG_F32) {
+            xin = rt.arena->matrix(M, E_, rt.dtype);
+            FG_LAUNCH("core", fg_cast_rows, x.ptr<float>(), (int)x.ld, xin.data, xin.dtype, (int)xin.ld, M, (int)E_, rt.stream);
+        }
+        Tensor z = gate_.forward(rt, xin, nullptr, Tensor(), FG_F32, false, nullptr, nullptr);
+        Tensor g = rt.arena->matrix(M, D_, rt.dtype);
+        FG_LAUNCH("core", fg_gelu_mul_gather, z.ptr<float>(), (int)z.ld, table_.t.data, table_.t.dtype, (int)table_.t.ld, (int)col_, b.tokens, g.data,
+                  g.dtype, (int)g.ld, M, (int)D_, rt.stream);
+        Tensor y = proj_.forward(rt, g, nullptr, Tensor(), FG_F32, false, nullptr, nullptr);
+        FG_LAUNCH("core", fg_norm_add_norm, y.ptr<float>(), norm_w_.t.ptr<float>(), x.ptr<float>(), nullptr, nullptr, rt.dtype, M, (int)E_, eps_, 0.f,
+                  rt.stream);
+    }
+
+private:
+    int64_t E_ = 0, V_ = 0, D_ = 0, col_ = 0, TD_ = 0;
+    float eps_ = 0.f;
+    Weight table_, norm_w_;
+    Linear gate_, proj_;
 };
 
 // ------------------------------------------------------------------------------------ stream maps
@@ -1180,7 +1264,7 @@ public:
 // ------------------------------------------------------------------------------------ registries
 static std::mutex g_parts_mutex;
 static std::map<std::string, PartFactory> &factories(int role) {
-    static std::map<std::string, PartFactory> r[8];
+    static std::map<std::string, PartFactory> r[9];
     static bool init = false;
     if (!init) {
         init = true;
@@ -1190,12 +1274,13 @@ static std::map<std::string, PartFactory> &factories(int role) {
         r[FG_ROLE_FEED_FORWARD]["swiglu"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<SwiGLU>(p); };
         r[FG_ROLE_EMBEDDING]["embedding"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<TokenEmbedding>(p); };
         r[FG_ROLE_HEAD]["lm_head"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<LMHead>(p); };
+        r[FG_ROLE_TOKEN_INPUT]["gated_token_embedding"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<GatedTokenEmbedding>(p); };
         r[FG_ROLE_STREAM_MAP]["concat_linear"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<ConcatLinear>(p); };
         add_recurrent_kinds(r[FG_ROLE_MIXER]);
         add_attention_kinds(r[FG_ROLE_MIXER]);
         add_expert_kinds(r[FG_ROLE_FEED_FORWARD]);
     }
-    if (role < 0 || role > 7) fail(FG_E_USAGE, format("role %d does not exist", role));
+    if (role < 0 || role > 8) fail(FG_E_USAGE, format("role %d does not exist", role));
     return r[role];
 }
 static std::map<std::string, BlockFactory> &block_factories() {

@@ -146,6 +146,13 @@ public:
                                  Tensor &residual, Norm *emit_norm) = 0;
 };
 
+// What a layer adds to the stream from the tokens themselves, behind its sublayers (a second embedding table read per layer).
+class TokenInput : public Part {
+public:
+    // x [M, E] float32 is updated in place; batch.tokens names the rows' tokens
+    virtual void forward(Runtime &rt, const Batch &batch, Tensor &x) = 0;
+};
+
 // An arrangement of a mixer, a feed-forward and their norms around the residual stream.  A layer may have no
 // feed-forward (feed_forward and its norms are then null); the post norms exist only in layers that give them.
 class Block {
@@ -155,6 +162,7 @@ public:
     FeedForward *feed_forward = nullptr;
     Norm *mixer_norm = nullptr, *feed_forward_norm = nullptr;
     Norm *mixer_post_norm = nullptr, *feed_forward_post_norm = nullptr;   // on a sublayer's output, before the residual add
+    TokenInput *token_input = nullptr;       // optional; the model runs it on the stream right behind the block
     // refuses a layer this arrangement cannot run (called once, when the model is built)
     virtual void check_layer() const;
     // true: the block hands the NEXT block's first norm over finished (xw = the normalised rows, tiles == 0) instead of
@@ -209,6 +217,8 @@ void register_external_part(int role, const std::string &kind, const fg_part_vta
 void add_recurrent_kinds(std::map<std::string, PartFactory> &mixers);
 void add_attention_kinds(std::map<std::string, PartFactory> &mixers);
 void add_expert_kinds(std::map<std::string, PartFactory> &feed_forwards);
+// the built-in gated feed-forward {hidden_size, d_ff} for parts that hold one inside (a shared expert)
+std::unique_ptr<FeedForward> make_swiglu(const Json &params);
 
 // a part's tensor by its local name (an internal error if the model did not hand it over)
 const Weight &tensor_of(const std::map<std::string, Weight> &tensors, const char *name);

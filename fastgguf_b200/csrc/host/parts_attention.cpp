@@ -11,6 +11,11 @@
 //     score = scale * (q . k), then softcap * tanh(score / softcap)
 //     a row sees itself and the window - 1 keys before it
 //     the softmax's denominator also holds exp(sink_h), a learned number per head
+//   and, as further options: the q/k norm per head with one weight vector [head_dim] for all heads of q and one for all heads
+//   of k ("qk_norm": "head"); rotated pairs (i, i + rotary_dim / 2) when the position part's layout is "halves"; a gate per
+//   head on the heads' outputs, o_h <- o_h * sigmoid(W_g h)_h with W_g [heads, hidden] ("gate": "head"); a bias on the output
+//   projection ("o_bias": true), stored as one more column of the output matrix that meets a column of ones, so the
+//   projection's own pass adds it.
 //
 // "latent_attention": keys and values are linear maps of ONE small latent per token, c = norm(W_dkv h)[0:kv_rank], plus a
 // rotated key part of rot_dim numbers that all heads share; queries pass through a latent of their own,
@@ -49,8 +54,16 @@ public:
         bias_ = flag(p, "bias");
         sink_ = flag(p, "sink");
         const Json &qn = p.get("qk_norm");
-        if (!qn.is_null() && !(qn.is_string() && qn.as_string() == "whole")) fail(FG_E_CONFIG, "sink_attention: qk_norm " + qn.dump() + " is not known (known: whole)");
+        if (!qn.is_null() && !(qn.is_string() && (qn.as_string() == "whole" || qn.as_string() == "head")))
+            fail(FG_E_CONFIG, "sink_attention: qk_norm " + qn.dump() + " is not known (known: whole, head)");
         qk_norm_ = !qn.is_null();
+        norm_per_head_ = qk_norm_ && qn.as_string() == "head";
+        const Json &gt = p.get("gate");
+        if (!gt.is_null() && !(gt.is_string() && gt.as_string() == "head")) fail(FG_E_CONFIG, "sink_attention: gate " + gt.dump() + " is not known (known: head)");
+        gate_ = !gt.is_null();
+        o_bias_ = flag(p, "o_bias");
+        // columns behind the heads' outputs that carry the output bias: as many as keep a row a multiple of 8 numbers
+        pad_ = o_bias_ ? 8 - (int)(((int64_t)H_ * hdv_) % 8) : 0;
         if (window_ < 0 || softcap_ < 0.f || taps_ < 0) fail(FG_E_CONFIG, "sink_attention: window, softcap and conv_taps cannot be negative");
         if (hdv_ > 512) fail(FG_E_CONFIG, format("sink_attention: v_head_dim %d exceeds 512, the largest the kernel takes", hdv_));
         if (((size_t)H_ * hd_ + (size_t)KV_ * (hd_ + hdv_)) * 4 > 200 * 1024) fail(FG_E_CONFIG, "sink_attention: a token's q, k and v exceed what the kernel holds in shared memory");
@@ -61,6 +74,8 @@ public:
             if (position_->head_dim() != hd_)
                 fail(FG_E_CONFIG, format("sink_attention: the position encoding is built for head_dim %d, the mixer has %d", position_->head_dim(), hd_));
             rot_dims_ = (int)param_int(pos.get("params"), "rotary_dim", hd_, me);
+            const Json &layout = pos.get("params").get("layout");
+            rot_halves_ = !(layout.is_string() && layout.as_string() == "adjacent");
         }
     }
     std::vector<TensorDecl> tensor_decls() const override {
@@ -71,8 +86,13 @@ public:
         if (taps_ > 0)
             for (auto &n : std::vector<std::pair<const char *, int64_t>>{{"q_conv.weight", Q}, {"k_conv.weight", K}, {"v_conv.weight", V}})
                 d.push_back({n.first, {n.second, (int64_t)taps_}, false, 0, 0.5f});
-        if (qk_norm_) { d.push_back({"q_norm.weight", {Q}, false, 1, 0.01f}); d.push_back({"k_norm.weight", {K}, false, 1, 0.01f}); }
+        if (qk_norm_) {
+            d.push_back({"q_norm.weight", {norm_per_head_ ? (int64_t)hd_ : Q}, false, 1, 0.01f});
+            d.push_back({"k_norm.weight", {norm_per_head_ ? (int64_t)hd_ : K}, false, 1, 0.01f});
+        }
         if (sink_) d.push_back({"sinks", {(int64_t)H_}, false, 0, 1.0f});
+        if (gate_) d.push_back({"g_proj.weight", {(int64_t)H_, E_}});
+        if (o_bias_) d.push_back({"o_proj.bias", {(int64_t)E_}});
         return d;
     }
     bool cache_request(CacheRequest *out) const override {
@@ -86,8 +106,28 @@ public:
     void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
         const Weight &q = tensor_of(tensors, "q_proj.weight"), &k = tensor_of(tensors, "k_proj.weight"), &v = tensor_of(tensors, "v_proj.weight");
         int dt = (q.t.dtype == k.t.dtype && k.t.dtype == v.t.dtype) ? q.t.dtype : FG_F32;
-        qkv_ = Linear(concat_rows({q, k, v}, dt, rt.stream));
-        o_ = Linear(tensor_of(tensors, "o_proj.weight"));
+        std::vector<Weight> rows = {q, k, v};
+        if (gate_) {
+            rows.push_back(tensor_of(tensors, "g_proj.weight"));        // the gate's rows ride in the same contraction
+            if (rows.back().t.dtype != dt) dt = FG_F32;
+        }
+        qkv_ = Linear(concat_rows(rows, dt, rt.stream));
+        if (o_bias_) {
+            // [W_o | b | 0 ...]: the bias as a column that meets the ones fg_head_gate writes behind the heads' outputs
+            const Weight &w = tensor_of(tensors, "o_proj.weight"), &b = tensor_of(tensors, "o_proj.bias");
+            const int odt = w.t.dtype == b.t.dtype ? w.t.dtype : FG_F32;
+            const Weight wc = w.t.dtype == odt ? w : concat_rows({w}, odt, rt.stream), bc = b.t.dtype == odt ? b : concat_rows({b}, odt, rt.stream);
+            const int64_t K0 = (int64_t)H_ * hdv_, K1 = K0 + pad_;
+            const size_t es = (size_t)elem_size(odt);
+            Weight wide = make_weight(E_, K1, odt, "output projection with its bias column");
+            FG_CUDA(cudaMemsetAsync(wide.t.data, 0, (size_t)E_ * K1 * es, rt.stream));
+            FG_CUDA(cudaMemcpy2DAsync(wide.t.data, (size_t)K1 * es, wc.t.data, (size_t)wc.t.ld * es, (size_t)K0 * es, (size_t)E_, cudaMemcpyDeviceToDevice, rt.stream));
+            FG_CUDA(cudaMemcpy2DAsync((char *)wide.t.data + (size_t)K0 * es, (size_t)K1 * es, bc.t.data, es, es, (size_t)E_, cudaMemcpyDeviceToDevice, rt.stream));
+            FG_CUDA(cudaStreamSynchronize(rt.stream));
+            o_ = Linear(wide);
+        } else {
+            o_ = Linear(tensor_of(tensors, "o_proj.weight"));
+        }
         auto three = [&](const char *a, const char *b, const char *c, int64_t cols) {
             Weight x = tensor_of(tensors, a), y = tensor_of(tensors, b), z = tensor_of(tensors, c);
             // row-major [channels, cols]: the three lie one after another
@@ -115,15 +155,16 @@ public:
         const int M = (int)proj.rows;
         Tensor q = rt.arena->matrix(M, (int64_t)H_ * hd_, rt.dtype);
         const float *bias = bias_ ? bias_w_.t.ptr<float>() : nullptr;
-        FG_LAUNCH("mix", fg_qkv_prepare, proj.ptr<float>(), (int)proj.ld, bias, taps_ > 0 ? conv_w_.t.ptr<float>() : nullptr, taps_,
+        FG_LAUNCH("mix", fg_qkv_prepare_ext, proj.ptr<float>(), (int)proj.ld, bias, taps_ > 0 ? conv_w_.t.ptr<float>() : nullptr, taps_,
                   (const float *)io.state, qk_norm_ ? qn_w_.t.ptr<float>() : nullptr, qk_norm_ ? kn_w_.t.ptr<float>() : nullptr, eps_,
                   position_ ? position_->cos_table() : nullptr, position_ ? position_->sin_table() : nullptr, hd_ / 2, position_ ? rot_dims_ : 0,
                   b.positions, b.row_seq, b.cu_rows, b.slots, table, b.table_width, q.data, (int)q.ld, io.k_pool, io.v_pool, rt.dtype, M, H_, KV_,
-                  hd_, hdv_, io.page_size, rt.stream);
+                  hd_, hdv_, io.page_size, norm_per_head_ ? 1 : 0, rot_halves_ ? 1 : 0, rt.stream);
         if (taps_ > 1)
             FG_LAUNCH("mix", fg_conv_state_update, proj.ptr<float>(), (int)proj.ld, bias, taps_, (float *)io.state, b.cu_rows, b.slots, b.n_seq,
                       (int)channels(), rt.stream);
-        Tensor attn = rt.arena->matrix(M, (int64_t)H_ * hdv_, rt.dtype);
+        // (with an output bias the rows are wider than the heads' outputs: the columns behind them carry the ones)
+        Tensor attn = rt.arena->matrix(M, (int64_t)H_ * hdv_ + pad_, rt.dtype);
         const float *sinks = sink_ ? sinks_w_.t.ptr<float>() : nullptr;
         // bfloat16 with head size 64 / 128 for keys and values alike: the tensor-core kernels (a decode step: mma.sync with the
         // pages split over a cluster; portions: tcgen05 tiles of 128 rows, or mma.sync tiles of 64 for a few rows)
@@ -148,15 +189,18 @@ public:
             FG_LAUNCH("core", fg_attention_generic_ext, q.data, (int)q.ld, attn.data, (int)attn.ld, rt.dtype, b.positions, b.row_seq, table,
                       b.table_width, io.k_pool, io.v_pool, M, H_, KV_, hd_, hdv_, io.page_size, scale_, window_, 0, softcap_, sinks, 0, rt.stream);
         }
+        if (gate_ || pad_ > 0)
+            FG_LAUNCH("mix", fg_head_gate, attn.data, (int)attn.ld, attn.dtype, gate_ ? proj.ptr<float>() + channels() : nullptr, (int)proj.ld, M, H_, hdv_,
+                      pad_, rt.stream);
         DeferredNorm started;
         o_.forward(rt, attn, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
         return started;
     }
 
 private:
-    int E_ = 0, H_ = 0, KV_ = 0, hd_ = 0, hdv_ = 0, window_ = 0, taps_ = 0, rot_dims_ = 0;
+    int E_ = 0, H_ = 0, KV_ = 0, hd_ = 0, hdv_ = 0, window_ = 0, taps_ = 0, rot_dims_ = 0, pad_ = 0;
     float scale_ = 1.f, softcap_ = 0.f, eps_ = 1e-6f;
-    bool bias_ = false, sink_ = false, qk_norm_ = false;
+    bool bias_ = false, sink_ = false, qk_norm_ = false, norm_per_head_ = false, rot_halves_ = false, gate_ = false, o_bias_ = false;
     PositionEncoding *position_ = nullptr;
     Linear qkv_, o_;
     Weight bias_w_, conv_w_, qn_w_, kn_w_, sinks_w_;

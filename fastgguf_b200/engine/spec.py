@@ -49,6 +49,8 @@ class LayerSpec:
     #: norms on a sublayer's output, before it joins the residual stream (block "sandwich")
     mixer_post_norm: Optional[PartSpec] = None
     feed_forward_post_norm: Optional[PartSpec] = None
+    #: what the layer adds to the stream from its tokens, behind its sublayers (role ``token_input``)
+    token_input: Optional[PartSpec] = None
 
     def to_json(self) -> dict:
         def opt(p):
@@ -59,6 +61,8 @@ class LayerSpec:
             j["mixer_post_norm"] = self.mixer_post_norm.to_json()
         if self.feed_forward_post_norm is not None:
             j["feed_forward_post_norm"] = self.feed_forward_post_norm.to_json()
+        if self.token_input is not None:
+            j["token_input"] = self.token_input.to_json()
         return j
 
 
@@ -110,7 +114,7 @@ class ModelSpec:
             hidden_size=j["hidden_size"], vocab_size=j["vocab_size"], max_positions=j["max_positions"],
             embedding=P(j["embedding"]), final_norm=P(j["final_norm"]), head=P(j["head"]),
             layers=[LayerSpec(l["block"], P(l["mixer"]), O(l.get("feed_forward")), P(l["mixer_norm"]), O(l.get("feed_forward_norm")),
-                              O(l.get("mixer_post_norm")), O(l.get("feed_forward_post_norm"))) for l in j["layers"]],
+                              O(l.get("mixer_post_norm")), O(l.get("feed_forward_post_norm")), O(l.get("token_input"))) for l in j["layers"]],
             schedule=[RunSpec(r["layer"], r.get("cache_from"), bool(r.get("reenter", False))) for r in j["schedule"]],
             reentry=O(j.get("reentry")),
             stop_token_ids=tuple(j.get("stop_token_ids") or ()), ignored_tensors=tuple(j.get("ignored_tensors") or ()),

@@ -18,9 +18,10 @@ from .config.base import ModelConfig
 from .config.llama import LlamaConfig
 from .config.zirivik import ZirivikConfig
 from .config.salulorn import SalulornConfig
+from .config.pirozen import PirozenConfig
 from .engine.spec import ModelSpec
 
-_CLASSES = {"LlamaForCausalLM": LlamaConfig, "Zirivik": ZirivikConfig, "Salulorn": SalulornConfig}
+_CLASSES = {"LlamaForCausalLM": LlamaConfig, "Zirivik": ZirivikConfig, "Salulorn": SalulornConfig, "Pirozen": PirozenConfig}
 _keep_alive = []
 
 
