@@ -13,7 +13,7 @@ from ctypes import (CFUNCTYPE, POINTER, Structure, byref, c_char, c_char_p, c_fl
                     c_uint64, c_void_p)
 
 FG_F32, FG_BF16, FG_F16, FG_I32, FG_I64 = 0, 1, 2, 3, 4
-ROLE = {"norm": 0, "position": 1, "mixer": 2, "feed_forward": 3, "block": 4, "embedding": 5, "head": 6}
+ROLE = {"norm": 0, "position": 1, "mixer": 2, "feed_forward": 3, "block": 4, "embedding": 5, "head": 6, "stream_map": 7, "token_input": 8}
 
 OK, E_USAGE, E_CONFIG, E_WEIGHTS, E_CACHE, E_CAPACITY, E_TOKEN, E_DEVICE, E_KERNEL, E_INTERNAL = range(10)
 

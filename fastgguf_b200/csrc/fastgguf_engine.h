@@ -233,7 +233,8 @@ int fg_plan_batches(int n_requests, int batch_size, char **json_out);
 /* Builds ONE part of `role` / `kind` from its parameters and the given tensors, runs it once and returns float32
  * results on the host.  norm: x [M, cols_in] -> out [M, cols_in].  feed_forward: xn = x (converted to the engine
  * dtype), adds into residual [M, cols_in].  head: xn = x -> out [M, cols_out].  embedding: tokens [M] -> out
- * [M, cols_out].  Mixers need a cache: see fg_engine_block_forward. */
+ * [M, cols_out].  token_input: tokens [M] and the stream x [M, cols_in] -> out, the updated stream.  Mixers need a cache:
+ * see fg_engine_block_forward. */
 int fg_part_run(int role, const char *kind, const char *params_json, int dtype, const fg_host_tensor *tensors,
                 int n_tensors, const int *tokens, const float *x, float *residual, float *out, int M, int cols_in,
                 int cols_out);

@@ -782,6 +782,14 @@ int fg_part_run(int role, const char *kind, const char *params_json, int dtype, 
             Tensor xo = arena.matrix(M, cols_out, FG_F32);
             dynamic_cast<Embedding &>(*part).forward(rt, batch, xo, nullptr);
             download(xo, out);
+        } else if (role == FG_ROLE_TOKEN_INPUT) {
+            NEED(tokens); NEED(x); NEED(out);
+            int *tok = (int *)arena.alloc((size_t)M * 4);
+            FG_CUDA(cudaMemcpy(tok, tokens, (size_t)M * 4, cudaMemcpyHostToDevice));
+            batch.tokens = tok;
+            Tensor xs = upload(x, M, cols_in, FG_F32);
+            dynamic_cast<TokenInput &>(*part).forward(rt, batch, xs);
+            download(xs, out);
         } else {
             fail(FG_E_USAGE, std::string("fg_part_run cannot run a ") + role_name(role) + " alone");
         }

@@ -48,7 +48,8 @@ def run_part(role: str, kind: str, params: dict, tensors: dict, dtype="bfloat16"
              out_cols: int = 0):
     """Build ONE part from its parameters and tensors, run it once on the GPU and return float32 numpy results
     (``fg_part_run``): norm: x [M, E] -> [M, E]; feed_forward: xn = x, returns residual + part(x); head: xn = x ->
-    [M, out_cols]; embedding: tokens [M] -> [M, out_cols].  Mixers need a cache: ``Engine.block_forward``."""
+    [M, out_cols]; embedding: tokens [M] -> [M, out_cols]; token_input: tokens [M] and the stream x [M, E] -> the updated
+    stream.  Mixers need a cache: ``Engine.block_forward``."""
     import json
 
     import numpy as np
@@ -59,7 +60,7 @@ def run_part(role: str, kind: str, params: dict, tensors: dict, dtype="bfloat16"
     if tokens is not None:
         tok_arr, M = capi.int_array(tokens)
         cols_in = 0
-    else:
+    if x is not None:
         x = np.ascontiguousarray(x, dtype=np.float32)
         M, cols_in = x.shape
     res = np.ascontiguousarray(residual, dtype=np.float32).copy() if residual is not None else None

@@ -112,7 +112,8 @@ def gated_expert(h, W, pre):
 def route(z, correction, r):
     """z [T, R] router logits -> (chosen [T, top] expert indices, weights [T, top])."""
     T, R = z.shape
-    top, count, keep = int(r["top"]), int(r["groups"]["count"]), int(r["groups"]["keep"])
+    groups = r.get("groups") or {"count": 1, "keep": 1}              # no groups: one group of everything, kept
+    top, count, keep = int(r["top"]), int(groups["count"]), int(groups.get("keep", groups["count"]))
     s = torch.softmax(z, -1)
     choice = s + correction
     per = R // count
@@ -122,7 +123,7 @@ def route(z, correction, r):
     choice = choice.masked_fill(~allowed.repeat_interleave(per, dim=1), float("-inf"))
     chosen = torch.topk(choice, top, dim=-1).indices
     w = torch.gather(s, 1, chosen)
-    w = w / (w.sum(-1, keepdim=True) + 1e-20) * float(r["scale"])
+    w = w / (w.sum(-1, keepdim=True) + 1e-20) * float(r.get("scale", 1.0))
     return chosen, w
 
 

@@ -1,0 +1,94 @@
+"""Seeded random Pirozen configurations, engine against the plain implementation: every size, head counts, key and value sizes,
+windows, rotated dimensions and their scaling, experts, groups, identity experts, the shared expert, layers without a
+feed-forward, the token input, the loop's span and count are drawn; then a batch of unequal prompts, portions, and decode steps
+during which sequences leave.  float32 engines are held to the float32 tolerance everywhere; bfloat16 engines run the same
+model with sharpened attention and every router output chosen."""
+import numpy as np
+import pytest
+
+from helpers import rel_err
+from pirozen_cases import attention, config, make_model, moe, without_choice
+from test_pirozen import TOL, engine_for, entry, plain_logits
+
+pytestmark = pytest.mark.gpu
+
+
+def draw_mlp(rng):
+    per, count = int(rng.choice([1, 2, 3, 4])), int(rng.choice([1, 2, 3, 4]))
+    outputs = per * count
+    identity = int(rng.integers(0, min(3, outputs))) if outputs > 1 else 0
+    keep = int(rng.integers(1, count + 1))
+    top = int(rng.integers(1, min(4, keep * per) + 1))
+    return moe(int(rng.choice([16, 24, 40, 64, 100])), outputs - identity, top, scale=float(rng.choice([1.0, 0.5, 1.5, 2.5])),
+               identity=identity if rng.random() < 0.8 or identity else None, groups=(count, keep) if count > 1 or rng.random() < 0.5 else None,
+               shared=None if rng.random() < 0.3 else int(rng.choice([16, 48, 72])))
+
+
+def draw_config(rng):
+    width = int(rng.choice([64, 96, 128, 160, 200, 72, 256]))
+    n_layers = int(rng.integers(1, 6))
+    layers = []
+    for _ in range(n_layers):
+        kv, dk = int(rng.choice([1, 2, 3])), int(rng.choice([16, 32, 64, 128, 24, 96]))
+        dv = dk if rng.random() < 0.6 else int(rng.choice([16, 40, 64, 96, 12]))
+        rot = None
+        if rng.random() < 0.85:
+            dims = int(rng.choice([d for d in (2, 8, 16, 24, 32, 64, 96, 128) if d <= dk]))
+            rot = (float(rng.choice([10.0, 1e4, 1e6])), dims)
+        scaling = None
+        if rot is not None and rng.random() < 0.6:
+            scaling = (float(rng.choice([2.0, 8.0, 40.0])), int(rng.choice([16, 64, 1024])), float(rng.choice([8.0, 32.0])), float(rng.choice([1.0, 0.5])))
+        mixer = attention(kv * int(rng.choice([1, 2, 3, 4])), kv, dk, dv, float(rng.uniform(0.05, 0.3)),
+                          size=None if rng.random() < 0.2 else int(rng.choice([1, 5, 17, 63, 64, 65, 100, 300])), rot=rot, scaling=scaling)
+        layers.append((mixer, None if rng.random() < 0.2 else draw_mlp(rng)))
+    loop = None
+    if rng.random() < 0.7:
+        start = int(rng.integers(0, n_layers))
+        loop = (start, int(rng.integers(start + 1, n_layers + 1)), int(rng.integers(1, 4)))
+    side = None if rng.random() < 0.25 else int(rng.choice([1, 4, 16, 20]))
+    return config(width, int(rng.integers(40, 500)), layers, loop=loop, side=side, eps=float(rng.choice([1e-5, 1e-6, 1e-3])))
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22, 23, 24])
+def test_random_configuration(tmp_path, seed):
+    rng = np.random.default_rng(seed)
+    case = draw_config(rng)
+    dtype = "bfloat16" if seed % 3 == 0 else "float32"
+    if dtype == "bfloat16":
+        case = without_choice(case)
+    d, W = make_model(tmp_path, case, seed, sharp=2.0 if dtype == "bfloat16" else 1.0)
+    B = int(rng.integers(1, 5))
+    total = [int(rng.integers(3, 200)) for _ in range(B)]
+    first = [int(rng.integers(1, t)) for t in total]
+    vocab = case["vocab"]
+    toks = [[int(t) for t in rng.integers(0, vocab, size=n)] for n in total]
+    want = [plain_logits(case, W, t) for t in toks]
+    eng = engine_for(d, dtype)
+    slots = [eng.acquire() for _ in toks]
+    got = eng.step_host([entry(s, t[:n]) for s, t, n in zip(slots, toks, first)])
+    row = 0
+    for b, n in enumerate(first):
+        for p in range(n):
+            assert rel_err(got[row], want[b][p]) < TOL[dtype], (seed, b, p)
+            row += 1
+    at = list(first)
+    # one more portion for the first sequence, then everyone token by token
+    if total[0] - at[0] > 3:
+        n = int(rng.integers(2, total[0] - at[0]))
+        got = eng.step_host([entry(slots[0], toks[0][at[0]:at[0] + n])])
+        for i in range(n):
+            assert rel_err(got[i], want[0][at[0] + i]) < TOL[dtype], (seed, "portion", at[0] + i)
+        at[0] += n
+    alive = [b for b in range(B) if at[b] < total[b]]
+    for b in [b for b in range(B) if at[b] == total[b]]:
+        eng.release(slots[b])
+    while alive:
+        got = eng.step_host([entry(slots[b], [toks[b][at[b]]]) for b in alive])
+        for i, b in enumerate(alive):
+            assert rel_err(got[i], want[b][at[b]]) < TOL[dtype], (seed, b, at[b])
+            at[b] += 1
+        for b in [b for b in alive if at[b] == total[b]]:
+            eng.release(slots[b])
+            alive.remove(b)
+    eng.cache.check()
+    assert eng.cache.live_slots() == []
