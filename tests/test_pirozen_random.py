@@ -6,9 +6,8 @@ model with sharpened attention and every router output chosen."""
 import numpy as np
 import pytest
 
-from helpers import rel_err
 from pirozen_cases import attention, config, make_model, moe, without_choice
-from test_pirozen import TOL, engine_for, entry, plain_logits
+from test_pirozen import Rows, conditioning, engine_for, entry, plain_logits
 
 pytestmark = pytest.mark.gpu
 
@@ -45,7 +44,9 @@ def draw_config(rng):
     if rng.random() < 0.7:
         start = int(rng.integers(0, n_layers))
         loop = (start, int(rng.integers(start + 1, n_layers + 1)), int(rng.integers(1, 4)))
-    side = None if rng.random() < 0.25 else int(rng.choice([1, 4, 16, 20]))
+    # (one number a token would make the normalised token input a fixed direction with a sign: tested alone, not here, where a
+    # gate near zero would flip it)
+    side = None if rng.random() < 0.25 else int(rng.choice([3, 4, 16, 20]))
     return config(width, int(rng.integers(40, 500)), layers, loop=loop, side=side, eps=float(rng.choice([1e-5, 1e-6, 1e-3])))
 
 
@@ -63,13 +64,14 @@ def test_random_configuration(tmp_path, seed):
     vocab = case["vocab"]
     toks = [[int(t) for t in rng.integers(0, vocab, size=n)] for n in total]
     want = [plain_logits(case, W, t) for t in toks]
+    rows = Rows(dtype, conditioning(d, case, W, toks, dtype))
     eng = engine_for(d, dtype)
     slots = [eng.acquire() for _ in toks]
     got = eng.step_host([entry(s, t[:n]) for s, t, n in zip(slots, toks, first)])
     row = 0
     for b, n in enumerate(first):
         for p in range(n):
-            assert rel_err(got[row], want[b][p]) < TOL[dtype], (seed, b, p)
+            rows.add(got[row], want[b][p], (seed, b, p), b, p)
             row += 1
     at = list(first)
     # one more portion for the first sequence, then everyone token by token
@@ -77,7 +79,7 @@ def test_random_configuration(tmp_path, seed):
         n = int(rng.integers(2, total[0] - at[0]))
         got = eng.step_host([entry(slots[0], toks[0][at[0]:at[0] + n])])
         for i in range(n):
-            assert rel_err(got[i], want[0][at[0] + i]) < TOL[dtype], (seed, "portion", at[0] + i)
+            rows.add(got[i], want[0][at[0] + i], (seed, "portion", at[0] + i), 0, at[0] + i)
         at[0] += n
     alive = [b for b in range(B) if at[b] < total[b]]
     for b in [b for b in range(B) if at[b] == total[b]]:
@@ -85,10 +87,11 @@ def test_random_configuration(tmp_path, seed):
     while alive:
         got = eng.step_host([entry(slots[b], [toks[b][at[b]]]) for b in alive])
         for i, b in enumerate(alive):
-            assert rel_err(got[i], want[b][at[b]]) < TOL[dtype], (seed, b, at[b])
+            rows.add(got[i], want[b][at[b]], (seed, b, at[b]), b, at[b])
             at[b] += 1
         for b in [b for b in alive if at[b] == total[b]]:
             eng.release(slots[b])
             alive.remove(b)
+    rows.done()
     eng.cache.check()
     assert eng.cache.live_slots() == []
