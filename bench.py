@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--model 1b|3b|8b] [--dtype bfloat16|float32]
                     [--layers L] [--no-points] [--no-prefill] [--impl reference]
-    python bench.py --compare zirivik|salulorn [--sizes s,m] [--steps K] [--warmup W] [--batch 8]
+    python bench.py --compare zirivik|salulorn|pirozen [--sizes s,m] [--steps K] [--warmup W] [--batch 8]
 
 Default run: the layer sizes of Llama 3.2 1B with random weights, bfloat16, a batch of 8 sequences with random
 prompts of unequal lengths 128..1024, context 4096.  ``--model 3b``: prompts 64..2048, context 4096; ``--model 8b``:
@@ -15,10 +15,11 @@ read (every weight once, the cache of the live requests) by its time; ``points``
 at the headline batch with the reference's default sampler instead of greedy; ``points_detail`` what each of them was
 made of.  Every step reads gigabytes of weights, far more than the 126 MB L2, so no flush is needed between timed steps.
 
-``--compare zirivik`` (or ``salulorn``) leaves all of that alone and prints another line: prefill (one step of 2,048 tokens)
-and decode (graph-replayed steps of a batch) of models of that design whose layers have the sizes of real models, beside Llama models
-of the same width, depth, heads and feed-forward size, with the device time of every launcher of one prefill step and
-of decode steps run eagerly (``profile``), so that like kernels can be set side by side.
+``--compare zirivik`` (or ``salulorn``, ``pirozen``) leaves all of that alone and prints another line: prefill (one step of
+2,048 tokens) and decode (graph-replayed steps of a batch) of models of that design whose layers have the sizes of real models,
+beside Llama models of the same width, depth, heads and feed-forward size (Pirozen: beside Zirivik models of windowed attention
+layers with experts of the same sizes, the closest the engine has), with the device time of every launcher of one prefill step
+and of decode steps run eagerly (``profile``), so that like kernels can be set side by side.
 """
 import argparse
 import json
@@ -168,7 +169,35 @@ def salulorn_config(width, heads, kv_heads, head_dim, ff, vocab, window, expert_
             "loop": {"start": 0, "stop": len(layers), "times": 1}}
 
 
-DESIGNS = {"zirivik": zirivik_config, "salulorn": salulorn_config}
+def pirozen_config(width, heads, kv_heads, head_dim, ff, vocab, window, expert_ff, blocks=2):
+    """Layers of a real model's sizes: windowed attention with a gate per head, half of a head rotated with blended
+    frequencies, beside eight experts and two identity outputs in two groups of which one stays, two a token, plus a shared
+    expert; a token input of 256 numbers a layer; the whole stack is a loop that runs once, so the loop's input map is part of
+    the step."""
+    del ff
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "mask": {"size": window},
+           "rot": {"base": 1000000.0, "dims": head_dim // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": expert_ff},
+           "router": {"experts": 8, "identity": 2, "top": 2, "scale": 2.0, "groups": {"count": 2, "keep": 1}}}
+    n = 4 * blocks
+    return {"architecture": "Pirozen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "token_side": {"dim": 256},
+            "layers": [{"type": "attention", "mixer": att, "mlp": moe} for _ in range(n)], "loop": {"start": 0, "stop": n, "times": 1}}
+
+
+def zirivik_attention_config(width, heads, kv_heads, head_dim, ff, vocab, window, expert_ff, blocks=2):
+    """The engine's closest model to Pirozen: Zirivik's windowed attention layers (four kept first keys), each with eight experts
+    of the same size, two a token."""
+    del ff
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+           "mask": {"size": window, "keep_first": 4}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
+    return {"architecture": "Zirivik", "vocab": vocab, "width": width, "embedding": {"scale": width ** 0.5}, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "layers": [{"type": "attention", "mixer": att, "mlp": moe} for _ in range(4 * blocks)]}
+
+
+DESIGNS = {"zirivik": zirivik_config, "salulorn": salulorn_config, "pirozen": pirozen_config}
+#: the model a design stands beside, where that is not Llama
+COUNTERPARTS = {"pirozen": ("zirivik", zirivik_attention_config)}
 
 #: name -> (width, heads, kv_heads, head_dim, ff, vocab, window, expert_ff)
 COMPARE_SIZES = {"s": (2048, 32, 8, 64, 8192, 32768, 1024, 2048), "m": (4096, 32, 8, 128, 14336, 32768, 2048, 4096)}
@@ -192,7 +221,10 @@ def compare_designs(args):
         llama = dict(LLAMA_3_2_1B, hidden_size=width, num_hidden_layers=len(z["layers"]), num_attention_heads=heads,
                      num_key_value_heads=kv, head_dim=hd, intermediate_size=ff, vocab_size=vocab, rope_scaling=None, bos_token_id=1, eos_token_id=2)
         row = {}
-        for label, cd in ((design, z), ("llama", llama)):
+        other = ("llama", llama)
+        if design in COUNTERPARTS:
+            other = (COUNTERPARTS[design][0], COUNTERPARTS[design][1](width, heads, kv, hd, ff, vocab, window, eff))
+        for label, cd in ((design, z), other):
             cfg = config_from_dict(cd)
             per_seq = (1024 + W + K * 3 + 128 + 63) // 64 * 64
             engine = Engine.from_random(cfg, 0, dtype=args.dtype, max_tokens=max(B * per_seq, PREFILL_TOKENS + 64) + 64 * B,
@@ -247,7 +279,11 @@ def compare_designs(args):
                                                                for r in prof_all]}
             del engine
         row["config"] = {"width": width, "heads": heads, "kv_heads": kv, "head_dim": hd, "ff": ff, "vocab": vocab, "window": window}
-        if design == "zirivik":
+        if design == "pirozen":
+            row["config"].update({"experts": "8 of ff %d and 2 identity outputs, 2 groups of which 1 stays, 2 a row, shared expert of ff %d" % (eff, eff),
+                                  "rotated": "%d of %d, blended frequencies" % (hd // 2, hd), "token_input": "256 numbers a layer",
+                                  "loop": "all layers, once", "beside": "Zirivik: windowed attention + 8 experts of ff %d, 2 a row" % eff})
+        elif design == "zirivik":
             row["config"].update({"experts": "8 of ff %d, 2 a row" % eff, "retention": "%d heads of 128 x 128" % (width // 128)})
         else:
             row["config"].update({"gla": "%d heads of 64 x 128" % (width // 128), "latent": "rank 512 + 64 rotated, queries through %d" % (width * 3 // 4),

@@ -354,7 +354,8 @@ extern "C" int fg_qkv_prepare(const float *proj, int ld, const float *bias, cons
 // projection adds the bias in the same pass.
 template <typename T>
 __global__ void head_gate_kernel(T *__restrict__ x, int ldx, const float *__restrict__ gate, int ldg, int H, int DV, int pad) {
-    pdl_launch_dependents();
+    // (no early release of the successor: this kernel stands between two tensor-memory contractions, and the second must not
+    // start beside the first while this one sits resident and waiting; the successor starts when this kernel has finished)
     pdl_wait();
     const int m = blockIdx.x;
     T *row = x + (size_t)m * ldx;

@@ -493,7 +493,8 @@ template <typename TO>
 __global__ void rmsnorm_pair_kernel(const float *__restrict__ x, const float *__restrict__ w_a, const float *__restrict__ w_b,
                                     TO *__restrict__ out_a, TO *__restrict__ out_b, int E, float eps_a, float eps_b) {
     __shared__ float scratch[32];
-    pdl_launch_dependents();
+    // (no early release of the successor: this kernel stands between two tensor-memory contractions, and the second must not
+    // start beside the first while this one sits resident and waiting; the successor starts when this kernel has finished)
     pdl_wait();
     const float *xi = x + (size_t)blockIdx.x * E;
     float ss = 0.f;
@@ -523,7 +524,8 @@ extern "C" int fg_rmsnorm_pair(const float *x, const float *w_a, const float *w_
 // out[m, c] = T(x[m, c]): the float32 stream itself (no norm) rounded to the activation dtype.
 template <typename T>
 __global__ void cast_rows_kernel(const float *__restrict__ x, int ldx, T *__restrict__ out, int ldo, size_t total, int E) {
-    pdl_launch_dependents();
+    // (no early release of the successor: this kernel stands between two tensor-memory contractions, and the second must not
+    // start beside the first while this one sits resident and waiting; the successor starts when this kernel has finished)
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -554,7 +556,8 @@ __device__ __forceinline__ float gelu_tanh_f32(float z) {
 template <typename TT, typename TO>
 __global__ void gelu_mul_gather_kernel(const float *__restrict__ z, int ldz, const TT *__restrict__ table, int ldt, int col0,
                                        const int *__restrict__ tokens, TO *__restrict__ out, int ldo, size_t total, int D) {
-    pdl_launch_dependents();
+    // (no early release of the successor: this kernel stands between two tensor-memory contractions, and the second must not
+    // start beside the first while this one sits resident and waiting; the successor starts when this kernel has finished)
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;

@@ -627,7 +627,8 @@ template <typename T>
 __global__ void moe_combine_weighted_kernel(const float *__restrict__ slot_out, int ld, const int *__restrict__ slot_of,
                                             const int *__restrict__ pair_expert, const float *__restrict__ pair_weight,
                                             const T *__restrict__ x, int ldx, int n_real, float *__restrict__ t, int top, int E, int accumulate) {
-    pdl_launch_dependents();
+    // (no early release of the successor: this kernel stands between two tensor-memory contractions, and the second must not
+    // start beside the first while this one sits resident and waiting; the successor starts when this kernel has finished)
     pdl_wait();
     const int r = blockIdx.x;
     for (int i = threadIdx.x; i < E; i += blockDim.x) {
