@@ -353,26 +353,43 @@ extern "C" int fg_qkv_prepare(const float *proj, int ld, const float *bias, cons
 // behind the heads are set to (1, 0, 0, ...): with the output projection's bias stored as column H * DV of its matrix, the
 // projection adds the bias in the same pass.
 template <typename T>
-__global__ void head_gate_kernel(T *__restrict__ x, int ldx, const float *__restrict__ gate, int ldg, int H, int DV, int pad) {
+__global__ void head_gate_kernel(T *__restrict__ x, int ldx, const float *__restrict__ gate, int ldg, int H, int DV, int pad, int vec) {
+    extern __shared__ float head_gate_sig[];        // the row's H gates
     // (no early release of the successor: this kernel stands between two tensor-memory contractions, and the second must not
     // start beside the first while this one sits resident and waiting; the successor starts when this kernel has finished)
     pdl_wait();
     const int m = blockIdx.x;
     T *row = x + (size_t)m * ldx;
-    if (gate)
-        for (int e = threadIdx.x; e < H * DV; e += blockDim.x) {
-            const float g = 1.0f / (1.0f + expf(-gate[(size_t)m * ldg + e / DV]));
-            row[e] = from_f32<T>(to_f32<T>(row[e]) * g);
+    if (gate) {
+        for (int h = threadIdx.x; h < H; h += blockDim.x) head_gate_sig[h] = 1.0f / (1.0f + expf(-gate[(size_t)m * ldg + h]));
+        __syncthreads();
+        if (vec) {
+            // 16 bytes a thread; DV is a multiple of the run, so a run lies in one head
+            constexpr int PER = 16 / sizeof(T);
+            for (int e = threadIdx.x * PER; e < H * DV; e += blockDim.x * PER) {
+                const float g = head_gate_sig[e / DV];
+                uint4 raw = *reinterpret_cast<const uint4 *>(row + e);
+                T *v = reinterpret_cast<T *>(&raw);
+#pragma unroll
+                for (int i = 0; i < PER; i++) v[i] = from_f32<T>(to_f32<T>(v[i]) * g);
+                *reinterpret_cast<uint4 *>(row + e) = raw;
+            }
+        } else {
+            for (int e = threadIdx.x; e < H * DV; e += blockDim.x) row[e] = from_f32<T>(to_f32<T>(row[e]) * head_gate_sig[e / DV]);
         }
+    }
     for (int e = threadIdx.x; e < pad; e += blockDim.x) row[H * DV + e] = from_f32<T>(e == 0 ? 1.0f : 0.0f);
 }
 
 extern "C" int fg_head_gate(void *x, int ldx, int dtype, const float *gate, int ldg, int M, int H, int DV, int pad, cudaStream_t stream) {
     if (M <= 0 || (!gate && pad <= 0)) return 0;
-    if (H * DV + pad > ldx) return FG_ERR_BAD_SIZE;
-    const int threads = H * DV >= 1024 ? 256 : 128;
-    if (dtype == FG_F32) return fg_launch(head_gate_kernel<float>, dim3(M), dim3(threads), 0, stream, (float *)x, ldx, gate, ldg, H, DV, pad);
-    if (dtype == FG_BF16) return fg_launch(head_gate_kernel<bf16>, dim3(M), dim3(threads), 0, stream, (bf16 *)x, ldx, gate, ldg, H, DV, pad);
+    if (H * DV + pad > ldx || H > 8192) return FG_ERR_BAD_SIZE;
+    const int threads = H * DV >= 4096 ? 256 : 128;
+    const size_t smem = (size_t)H * sizeof(float);
+    const int per = dtype == FG_F32 ? 4 : 8;
+    const int vec = (DV % per == 0 && ldx % per == 0 && ((uintptr_t)x & 15) == 0) ? 1 : 0;
+    if (dtype == FG_F32) return fg_launch(head_gate_kernel<float>, dim3(M), dim3(threads), smem, stream, (float *)x, ldx, gate, ldg, H, DV, pad, vec);
+    if (dtype == FG_BF16) return fg_launch(head_gate_kernel<bf16>, dim3(M), dim3(threads), smem, stream, (bf16 *)x, ldx, gate, ldg, H, DV, pad, vec);
     return FG_ERR_BAD_DTYPE;
 }
 

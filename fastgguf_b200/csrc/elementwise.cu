@@ -485,23 +485,51 @@ extern "C" int fg_concat2(const float *a, int lda, const float *b, int ldb, void
     return FG_ERR_BAD_DTYPE;
 }
 
+// four neighbours stored at once (16 bytes of float32, 8 bytes of bfloat16; the address is a multiple of that)
+__device__ __forceinline__ void store4(float *o, float a, float b, float c, float d) { *reinterpret_cast<float4 *>(o) = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(bf16 *o, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 raw;
+    raw.x = *reinterpret_cast<unsigned *>(&lo);
+    raw.y = *reinterpret_cast<unsigned *>(&hi);
+    *reinterpret_cast<uint2 *>(o) = raw;
+}
+
 // ------------------------------------------------------------------ two norms of the same rows
 // Blocks whose two sublayers each normalise the SAME stream with a weight of their own: out_a = x / rms(x) * w_a and
 // out_b = x / rms(x) * w_b (one statistic when the eps agree, which is the case the kernel is for; two otherwise), one pass
 // over the row.  Statistics are 32-bit; one block a row, fixed reduction order.
 template <typename TO>
 __global__ void rmsnorm_pair_kernel(const float *__restrict__ x, const float *__restrict__ w_a, const float *__restrict__ w_b,
-                                    TO *__restrict__ out_a, TO *__restrict__ out_b, int E, float eps_a, float eps_b) {
+                                    TO *__restrict__ out_a, TO *__restrict__ out_b, int E, float eps_a, float eps_b, int vec) {
     __shared__ float scratch[32];
     // (no early release of the successor: this kernel stands between two tensor-memory contractions, and the second must not
     // start beside the first while this one sits resident and waiting; the successor starts when this kernel has finished)
     pdl_wait();
     const float *xi = x + (size_t)blockIdx.x * E;
+    TO *oa = out_a + (size_t)blockIdx.x * E, *ob = out_b + (size_t)blockIdx.x * E;
+    if (vec) {
+        // four neighbours a thread and pass (16-byte loads of the row and of both weights); the order in which the squares are
+        // added depends on E alone
+        float ss = 0.f;
+        for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(xi + i);
+            ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+        }
+        ss = block_sum(ss, scratch);
+        const float inv_a = 1.0f / sqrtf(ss / (float)E + eps_a), inv_b = 1.0f / sqrtf(ss / (float)E + eps_b);
+        for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(xi + i);
+            const float4 a = *reinterpret_cast<const float4 *>(w_a + i), b = *reinterpret_cast<const float4 *>(w_b + i);
+            store4(oa + i, v.x * inv_a * a.x, v.y * inv_a * a.y, v.z * inv_a * a.z, v.w * inv_a * a.w);
+            store4(ob + i, v.x * inv_b * b.x, v.y * inv_b * b.y, v.z * inv_b * b.z, v.w * inv_b * b.w);
+        }
+        return;
+    }
     float ss = 0.f;
     for (int i = threadIdx.x; i < E; i += blockDim.x) { float v = xi[i]; ss += v * v; }
     ss = block_sum(ss, scratch);
     const float inv_a = 1.0f / sqrtf(ss / (float)E + eps_a), inv_b = 1.0f / sqrtf(ss / (float)E + eps_b);
-    TO *oa = out_a + (size_t)blockIdx.x * E, *ob = out_b + (size_t)blockIdx.x * E;
     for (int i = threadIdx.x; i < E; i += blockDim.x) {
         const float v = xi[i];
         oa[i] = from_f32<TO>(v * inv_a * w_a[i]);
@@ -513,22 +541,37 @@ extern "C" int fg_rmsnorm_pair(const float *x, const float *w_a, const float *w_
                                float eps_a, float eps_b, cudaStream_t stream) {
     if (R <= 0) return 0;
     const int threads = E >= 4096 ? 512 : (E >= 1024 ? 256 : (E >= 256 ? 128 : 64));
+    const int vec = (E % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)w_a) | ((uintptr_t)w_b) | ((uintptr_t)out_a) | ((uintptr_t)out_b)) & 15) == 0) ? 1 : 0;
     if (out_dtype == FG_F32)
-        return fg_launch(rmsnorm_pair_kernel<float>, dim3(R), dim3(threads), 0, stream, x, w_a, w_b, (float *)out_a, (float *)out_b, E, eps_a, eps_b);
+        return fg_launch(rmsnorm_pair_kernel<float>, dim3(R), dim3(threads), 0, stream, x, w_a, w_b, (float *)out_a, (float *)out_b, E, eps_a, eps_b,
+                         vec);
     if (out_dtype == FG_BF16)
-        return fg_launch(rmsnorm_pair_kernel<bf16>, dim3(R), dim3(threads), 0, stream, x, w_a, w_b, (bf16 *)out_a, (bf16 *)out_b, E, eps_a, eps_b);
+        return fg_launch(rmsnorm_pair_kernel<bf16>, dim3(R), dim3(threads), 0, stream, x, w_a, w_b, (bf16 *)out_a, (bf16 *)out_b, E, eps_a, eps_b,
+                         vec);
     return FG_ERR_BAD_DTYPE;
 }
 
 // ------------------------------------------------------------------ the stream as a contraction's input
 // out[m, c] = T(x[m, c]): the float32 stream itself (no norm) rounded to the activation dtype.
 template <typename T>
-__global__ void cast_rows_kernel(const float *__restrict__ x, int ldx, T *__restrict__ out, int ldo, size_t total, int E) {
+__global__ void cast_rows_kernel(const float *__restrict__ x, int ldx, T *__restrict__ out, int ldo, size_t total, int E, int vec) {
     // (no early release of the successor: this kernel stands between two tensor-memory contractions, and the second must not
     // start beside the first while this one sits resident and waiting; the successor starts when this kernel has finished)
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
+    if (vec) {
+        // four neighbours of a row a thread: one 16-byte load
+        const size_t quads = total / 4;
+        const int per_row = E / 4;
+        for (; i < quads; i += stride) {
+            const size_t m = i / (size_t)per_row;
+            const int c = (int)(i - m * (size_t)per_row) * 4;
+            const float4 v = *reinterpret_cast<const float4 *>(x + m * ldx + c);
+            store4(out + m * ldo + c, v.x, v.y, v.z, v.w);
+        }
+        return;
+    }
     for (; i < total; i += stride) {
         const size_t m = i / (size_t)E;
         const int c = (int)(i - m * (size_t)E);
@@ -539,10 +582,11 @@ __global__ void cast_rows_kernel(const float *__restrict__ x, int ldx, T *__rest
 extern "C" int fg_cast_rows(const float *x, int ldx, void *out, int out_dtype, int ldo, int M, int E, cudaStream_t stream) {
     const size_t total = (size_t)M * (size_t)E;
     if (total == 0) return 0;
-    const size_t want = (total + 255) / 256;
+    const int vec = (E % 4 == 0 && ldx % 4 == 0 && ldo % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)out)) & 15) == 0) ? 1 : 0;
+    const size_t want = ((vec ? total / 4 : total) + 255) / 256;
     const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
-    if (out_dtype == FG_F32) return fg_launch(cast_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, ldx, (float *)out, ldo, total, E);
-    if (out_dtype == FG_BF16) return fg_launch(cast_rows_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, ldx, (bf16 *)out, ldo, total, E);
+    if (out_dtype == FG_F32) return fg_launch(cast_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, ldx, (float *)out, ldo, total, E, vec);
+    if (out_dtype == FG_BF16) return fg_launch(cast_rows_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, ldx, (bf16 *)out, ldo, total, E, vec);
     return FG_ERR_BAD_DTYPE;
 }
 

@@ -141,7 +141,10 @@ extern "C" int fg_moe_route(const float *logits, int M, int X, int top, int *pai
 // the `keep` best groups can be chosen (the others count as minus infinity, whatever sign c has).  The `top` outputs with the
 // largest c are taken (ties to the lower index); their weights are s / (sum of the chosen s + 1e-20) * scale.  Outputs at and
 // beyond n_real have no expert behind them (the caller gives them a meaning, e.g. "the input itself"); they are routed,
-// grouped and counted like the others.  One block; a thread a row.  logits: [M, X] float32.
+// grouped and counted like the others.  One block; a thread a row.  logits: [M, X] float32.  CACHED: the row's X scores are
+// formed once and kept in shared memory ([X][threads], so that a warp's accesses fall into different banks); otherwise every
+// use forms them again (the same operations, the same values).
+template <bool CACHED>
 __global__ void __launch_bounds__(1024)
 moe_route_grouped_kernel(const float *__restrict__ logits, const float *__restrict__ bias, int M, int X, int top, int n_groups, int keep,
                          float scale, int *__restrict__ pair_expert, float *__restrict__ pair_weight, int *__restrict__ offsets,
@@ -152,13 +155,23 @@ moe_route_grouped_kernel(const float *__restrict__ logits, const float *__restri
     for (int e = threadIdx.x; e < X; e += blockDim.x) counts[e] = 0;
     __syncthreads();
     const int per = X / n_groups;
+    extern __shared__ float route_scores[];
+    float *sc = route_scores + threadIdx.x;
+    const int B = blockDim.x;
     for (int r = threadIdx.x; r < M; r += blockDim.x) {
         const float *z = logits + (size_t)r * X;
         float zmax = z[0];
         for (int e = 1; e < X; e++) zmax = fmaxf(zmax, z[e]);
         float sum = 0.f;
-        for (int e = 0; e < X; e++) sum += expf(z[e] - zmax);
+        for (int e = 0; e < X; e++) {
+            const float x = expf(z[e] - zmax);
+            if (CACHED) sc[e * B] = x;
+            sum += x;
+        }
         const float inv = 1.0f / sum;
+        if (CACHED)
+            for (int e = 0; e < X; e++) sc[e * B] *= inv;
+        auto score = [&](int e) { return CACHED ? sc[e * B] : expf(z[e] - zmax) * inv; };
         // the groups that stay: `keep` times the best group not yet taken
         unsigned long long allowed = 0ull;
         for (int k = 0; k < keep; k++) {
@@ -167,7 +180,7 @@ moe_route_grouped_kernel(const float *__restrict__ logits, const float *__restri
             for (int g = 0; g < n_groups; g++) {
                 if (allowed >> g & 1ull) continue;
                 float gs = -INFINITY;
-                for (int e = g * per; e < (g + 1) * per; e++) gs = fmaxf(gs, expf(z[e] - zmax) * inv + (bias ? bias[e] : 0.f));
+                for (int e = g * per; e < (g + 1) * per; e++) gs = fmaxf(gs, score(e) + (bias ? bias[e] : 0.f));
                 if (best < 0 || gs > bs) { best = g; bs = gs; }
             }
             allowed |= 1ull << best;
@@ -182,8 +195,8 @@ moe_route_grouped_kernel(const float *__restrict__ logits, const float *__restri
                 bool taken = false;
                 for (int q = 0; q < k; q++) taken = taken || chosen[q] == e;
                 if (taken) continue;
-                const float sc = expf(z[e] - zmax) * inv, c = sc + (bias ? bias[e] : 0.f);
-                if (best < 0 || c > bc) { best = e; bc = c; bsc = sc; }
+                const float se = score(e), c = se + (bias ? bias[e] : 0.f);
+                if (best < 0 || c > bc) { best = e; bc = c; bsc = se; }
             }
             chosen[k] = best;
             s_of[k] = bsc;
@@ -217,7 +230,18 @@ extern "C" int fg_moe_route_grouped(const float *logits, const float *bias, int 
         keep > n_groups || top > keep * (X / n_groups))
         return FG_ERR_BAD_SIZE;
     int threads = M >= 1024 ? 1024 : ((M + 31) / 32) * 32;
-    return fg_launch(moe_route_grouped_kernel, dim3(1), dim3(threads), 0, stream, logits, bias, M, X, top, n_groups, keep, scale, pair_expert,
+    const size_t smem = (size_t)X * threads * sizeof(float);
+    if (smem <= 160 * 1024) {
+        static bool raised = false;
+        if (!raised) {
+            cudaError_t e = cudaFuncSetAttribute(moe_route_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            raised = true;
+        }
+        return fg_launch(moe_route_grouped_kernel<true>, dim3(1), dim3(threads), smem, stream, logits, bias, M, X, top, n_groups, keep, scale,
+                         pair_expert, pair_weight, offsets, order, slot_of);
+    }
+    return fg_launch(moe_route_grouped_kernel<false>, dim3(1), dim3(threads), 0, stream, logits, bias, M, X, top, n_groups, keep, scale, pair_expert,
                      pair_weight, offsets, order, slot_of);
 }
 
@@ -626,20 +650,45 @@ extern "C" int fg_moe_combine(const float *slot_out, int ld, const int *slot_of,
 template <typename T>
 __global__ void moe_combine_weighted_kernel(const float *__restrict__ slot_out, int ld, const int *__restrict__ slot_of,
                                             const int *__restrict__ pair_expert, const float *__restrict__ pair_weight,
-                                            const T *__restrict__ x, int ldx, int n_real, float *__restrict__ t, int top, int E, int accumulate) {
+                                            const T *__restrict__ x, int ldx, int n_real, float *__restrict__ t, int top, int E, int accumulate,
+                                            int vec) {
+    // the row's choices once: where each one's output lies (null: the row's own input) and its weight
+    __shared__ const float *src[MOE_MAX_TOP];
+    __shared__ float wt[MOE_MAX_TOP];
     // (no early release of the successor: this kernel stands between two tensor-memory contractions, and the second must not
     // start beside the first while this one sits resident and waiting; the successor starts when this kernel has finished)
     pdl_wait();
     const int r = blockIdx.x;
+    if (threadIdx.x < top) {
+        const int p = r * top + threadIdx.x;
+        src[threadIdx.x] = pair_expert[p] < n_real ? slot_out + (size_t)slot_of[p] * ld : nullptr;
+        wt[threadIdx.x] = pair_weight[p];
+    }
+    __syncthreads();
+    const T *xr = x + (size_t)r * ldx;
+    float *tr = t + (size_t)r * E;
+    if (vec) {
+        // four neighbours a thread: 16-byte loads of the experts' outputs and of the sum
+        for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < top; k++) {
+                float4 v;
+                if (src[k]) v = *reinterpret_cast<const float4 *>(src[k] + i);
+                else v = make_float4(to_f32<T>(xr[i]), to_f32<T>(xr[i + 1]), to_f32<T>(xr[i + 2]), to_f32<T>(xr[i + 3]));
+                const float w = wt[k];
+                s.x = fmaf(w, v.x, s.x); s.y = fmaf(w, v.y, s.y); s.z = fmaf(w, v.z, s.z); s.w = fmaf(w, v.w, s.w);
+            }
+            float4 *o = reinterpret_cast<float4 *>(tr + i);
+            if (accumulate) { const float4 a = *o; s.x += a.x; s.y += a.y; s.z += a.z; s.w += a.w; }
+            *o = s;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < E; i += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top; k++) {
-            const int p = r * top + k;
-            const float v = pair_expert[p] < n_real ? slot_out[(size_t)slot_of[p] * ld + i] : to_f32<T>(x[(size_t)r * ldx + i]);
-            s = fmaf(pair_weight[p], v, s);
-        }
-        if (accumulate) t[(size_t)r * E + i] += s;
-        else t[(size_t)r * E + i] = s;
+        for (int k = 0; k < top; k++) s = fmaf(wt[k], src[k] ? src[k][i] : to_f32<T>(xr[i]), s);
+        if (accumulate) tr[i] += s;
+        else tr[i] = s;
     }
 }
 
@@ -647,12 +696,14 @@ extern "C" int fg_moe_combine_weighted(const float *slot_out, int ld, const int 
                                        const void *x, int ldx, int dtype, int n_real, float *t, int M, int top, int E, int accumulate,
                                        cudaStream_t stream) {
     if (M <= 0) return 0;
+    if (top <= 0 || top > MOE_MAX_TOP) return FG_ERR_BAD_SIZE;
     const int threads = E >= 1024 ? 256 : 128;
+    const int vec = (E % 4 == 0 && ld % 4 == 0 && ((uintptr_t)slot_out & 15) == 0 && ((uintptr_t)t & 15) == 0) ? 1 : 0;
     if (dtype == FG_F32)
         return fg_launch(moe_combine_weighted_kernel<float>, dim3(M), dim3(threads), 0, stream, slot_out, ld, slot_of, pair_expert, pair_weight,
-                         (const float *)x, ldx, n_real, t, top, E, accumulate);
+                         (const float *)x, ldx, n_real, t, top, E, accumulate, vec);
     if (dtype == FG_BF16)
         return fg_launch(moe_combine_weighted_kernel<bf16>, dim3(M), dim3(threads), 0, stream, slot_out, ld, slot_of, pair_expert, pair_weight,
-                         (const bf16 *)x, ldx, n_real, t, top, E, accumulate);
+                         (const bf16 *)x, ldx, n_real, t, top, E, accumulate, vec);
     return FG_ERR_BAD_DTYPE;
 }

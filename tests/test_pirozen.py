@@ -270,6 +270,7 @@ ROUTERS = {
     "eight groups of two, three kept": moe(16, 16, 3, scale=2.5, groups=(8, 3)),
     "groups of one": moe(24, 5, 2, identity=1, groups=(6, 2), shared=8),
     "many rows an expert": moe(48, 3, 2, scale=1.1, groups=(3, 2)),
+    "many outputs": moe(8, 44, 3, scale=1.3, identity=4, groups=(6, 3), shared=16),
 }
 
 
@@ -282,7 +283,8 @@ def test_router_and_experts_alone(name):
     Wb = random_weights(case, 31)
     W = {k: v.double() for k, v in Wb.items()}
     g = torch.Generator().manual_seed(32)
-    for rows in (3, 150, 700):
+    # (many outputs and more than a thousand rows: the routing kernel's form that keeps no scores)
+    for rows in (3, 150, 700) + ((1100,) if name == "many outputs" else ()):
         h = torch.randn(rows, 80, generator=g, dtype=torch.float64)
         want = pp.moe(h, W, "l0.mlp.", mlp).numpy()
         got = run_moe(mlp, Wb, h)
@@ -595,6 +597,28 @@ def test_a_far_token_is_remembered_without_a_window_only(tmp_path):
             assert rel_err(got[0], plain_logits(case, W, toks)[-1]) < TOL["float32"]
         gap = np.abs(last[0] - last[1]).max() / np.abs(last[0]).max()
         assert (gap > 1e-4) if differs else (gap < 1e-6), (size, gap)
+
+
+def test_many_prompt_steps_back_to_back():
+    """Forty prompt steps of 2,048 tokens one after another at sizes where every contraction runs on the tensor cores and the
+    small kernels between them (casts, gates, combines) are short against them: every step ends, with the same logits."""
+    from fastgguf_b200.engine.api import Engine
+    from fastgguf_b200.registry import config_from_dict
+    att = attention(16, 4, 64, 64, 0.125, size=512, rot=(1000000.0, 32), scaling=(8.0, 4096, 32.0, 1.0))
+    mlp = moe(1024, 6, 2, scale=2.0, identity=2, groups=(2, 1), shared=1024)
+    case = config(1024, 4096, [(att, mlp)] * 4, loop=(0, 4, 1), side=128, eps=1e-6)
+    eng = Engine.from_random(config_from_dict(case), 3, dtype="bfloat16", max_tokens=4096, max_batch=2, max_seq_len=4096)
+    toks = tokens_for(case, 2048, 90)
+    first = None
+    for _ in range(40):
+        s = eng.acquire()
+        got = eng.step_host([entry(s, toks, [2047])])
+        eng.release(s)
+        assert np.isfinite(got).all()
+        if first is None:
+            first = got
+        assert np.array_equal(got, first)
+    eng.cache.check()
 
 
 # ------------------------------------------------------------------------------ generation through the entry point
