@@ -44,11 +44,15 @@
  *                                   checkpoint}   a decay per key channel and token, sigmoid(low-rank(h) + b)^(1/tau); state as
  *                                   retention's; tensors q/k/v/g/o_proj.weight, decay_down/up.weight, decay_up.bias, norm.weight
  *                 "sink_attention" {hidden_size, n_heads, n_kv_heads, head_dim, v_head_dim, scale, window: 0, softcap: 0,
- *                                   conv_taps: 0, bias: false, sink: false, qk_norm: null | "whole", eps, position: PART | null}
+ *                                   conv_taps: 0, bias: false, o_bias: false, sink: false, qk_norm: null | "whole" | "head",
+ *                                   gate: null | "head", eps, position: PART | null}
  *                                   grouped-query attention with biases, a short convolution over time (its last inputs are
- *                                   per-sequence state), norms over the whole of q and of k, adjacent-pair rotation, capped
- *                                   scores and a sink; tensors q/k/v/o_proj.weight, q/k/v_proj.bias, q/k/v_conv.weight,
- *                                   q/k_norm.weight, sinks
+ *                                   per-sequence state), norms over the whole of q and of k ("whole": weights [heads * head_dim])
+ *                                   or per head ("head": one weight [head_dim] for all heads), rotation in the position part's
+ *                                   layout (adjacent pairs, or halves of the rotated part), capped scores, a sink, a sigmoid
+ *                                   gate per head from the mixer's input ("head": g_proj.weight [heads, hidden]); tensors
+ *                                   q/k/v/o_proj.weight, q/k/v_proj.bias, o_proj.bias, q/k/v_conv.weight, q/k_norm.weight,
+ *                                   sinks, g_proj.weight
  *                 "latent_attention" {hidden_size, n_heads, head_dim, rot_dim, v_head_dim, kv_rank, q_rank, scale, eps,
  *                                   sink: false, gate: false, position: PART}   keys and values from one latent a token plus a
  *                                   shared rotated key part (only those are cached); tensors q_down/q_up/kv_down/k_up/v_up/
@@ -57,6 +61,13 @@
  *                 "mlp"            {hidden_size, d_ff, activation: "relu2"}   down(act(up x))
  *                 "moe"            {hidden_size, d_ff, n_experts, top_k, limit, alpha: 1.702, router: "sigmoid_input"}
  *                                   tensors router.weight, experts.<e>.gate/up/down_proj.weight
+ *                                  {hidden_size, d_ff, n_experts, top_k, router: "softmax_grouped", n_identity: 0, n_groups: 1,
+ *                                   keep_groups: n_groups, route_scale: 1.0, shared_d_ff: 0}   softmax scores over n_experts +
+ *                                   n_identity outputs; the choice on score + router.bias among the keep_groups best of n_groups
+ *                                   groups of neighbours; weights = chosen scores / their sum * route_scale on the experts'
+ *                                   outputs; the last n_identity outputs return the input; experts silu(gate) * up; a shared
+ *                                   expert on every row; tensors router.weight, router.bias, experts.<e>.*, shared.gate/up/
+ *                                   down_proj.weight
  *   block         "prenorm"        x += mixer(norm1(x)); x += feed_forward(norm2(x))
  *                 "sandwich"       x += post1(mixer(norm1(x))); x += post2(feed_forward(norm2(x)))
  *                 "parallel"       x += mixer(norm1(x)) + feed_forward(norm1(x)), or, with a feed_forward_norm,

@@ -121,6 +121,30 @@ def test_rotary_tables_in_the_halves_layout(scaling):
         assert (c - c0).abs().max() > 0.05
 
 
+def test_rotary_tables_over_random_parameters():
+    """Two hundred drawn sets of base, rotated dimensions, factor, original length and the two turn counts - also ones whose ramp
+    is empty, starts below zero or ends beyond the last dimension, and a factor of one: the tables follow the plain formulas."""
+    from fastgguf_b200.parts import position_tables
+    rng = np.random.default_rng(0)
+    for _ in range(200):
+        dims = int(rng.choice([2, 4, 8, 16, 24, 32, 64, 128]))
+        hd = int(rng.choice([d for d in (2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 256) if d >= dims]))
+        base = float(rng.choice([2.0, 10.0, 100.0, 1e4, 5e5, 1e6]))
+        rot = {"base": base, "dims": dims}
+        params = {"head_dim": hd, "theta": base, "rotary_dim": dims, "layout": "halves", "scaling": None}
+        if rng.random() < 0.85:
+            sc = (float(rng.choice([1.0, 1.5, 2.0, 4.0, 8.0, 32.0, 64.0])), float(rng.choice([8, 16, 64, 256, 1024, 4096, 32768])),
+                  float(rng.choice([1.0, 4.0, 8.0, 32.0, 64.0])), float(rng.choice([0.25, 0.5, 1.0, 2.0, 32.0])))
+            rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), sc))
+            params["scaling"] = {"rope_type": "yarn", "factor": sc[0], "original_max_position_embeddings": sc[1], "beta_fast": sc[2],
+                                 "beta_slow": sc[3]}
+        cos, sin, _ = position_tables("rope", params, 150)
+        c, s = pp.rotary_table(rot, torch.arange(150))
+        h = dims // 2
+        assert np.abs(cos[:, :h] - c.numpy()).max() < 3e-6 and np.abs(sin[:, :h] - s.numpy()).max() < 3e-6, rot
+        assert np.all(cos[:, h:] == 1.0) and np.all(sin[:, h:] == 0.0)
+
+
 def one_layer(layer, mlp=None, width=80, vocab=50, side=None):
     return config(width, vocab, [(layer, mlp)], side=side)
 
