@@ -485,16 +485,6 @@ extern "C" int fg_concat2(const float *a, int lda, const float *b, int ldb, void
     return FG_ERR_BAD_DTYPE;
 }
 
-// four neighbours stored at once (16 bytes of float32, 8 bytes of bfloat16; the address is a multiple of that)
-__device__ __forceinline__ void store4(float *o, float a, float b, float c, float d) { *reinterpret_cast<float4 *>(o) = make_float4(a, b, c, d); }
-__device__ __forceinline__ void store4(bf16 *o, float a, float b, float c, float d) {
-    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
-    uint2 raw;
-    raw.x = *reinterpret_cast<unsigned *>(&lo);
-    raw.y = *reinterpret_cast<unsigned *>(&hi);
-    *reinterpret_cast<uint2 *>(o) = raw;
-}
-
 // ------------------------------------------------------------------ two norms of the same rows
 // Blocks whose two sublayers each normalise the SAME stream with a weight of their own: out_a = x / rms(x) * w_a and
 // out_b = x / rms(x) * w_b (one statistic when the eps agree, which is the case the kernel is for; two otherwise), one pass
@@ -521,8 +511,8 @@ __global__ void rmsnorm_pair_kernel(const float *__restrict__ x, const float *__
         for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
             const float4 v = *reinterpret_cast<const float4 *>(xi + i);
             const float4 a = *reinterpret_cast<const float4 *>(w_a + i), b = *reinterpret_cast<const float4 *>(w_b + i);
-            store4(oa + i, v.x * inv_a * a.x, v.y * inv_a * a.y, v.z * inv_a * a.z, v.w * inv_a * a.w);
-            store4(ob + i, v.x * inv_b * b.x, v.y * inv_b * b.y, v.z * inv_b * b.z, v.w * inv_b * b.w);
+            store4<TO>(oa + i, v.x * inv_a * a.x, v.y * inv_a * a.y, v.z * inv_a * a.z, v.w * inv_a * a.w);
+            store4<TO>(ob + i, v.x * inv_b * b.x, v.y * inv_b * b.y, v.z * inv_b * b.z, v.w * inv_b * b.w);
         }
         return;
     }
@@ -568,7 +558,7 @@ __global__ void cast_rows_kernel(const float *__restrict__ x, int ldx, T *__rest
             const size_t m = i / (size_t)per_row;
             const int c = (int)(i - m * (size_t)per_row) * 4;
             const float4 v = *reinterpret_cast<const float4 *>(x + m * ldx + c);
-            store4(out + m * ldo + c, v.x, v.y, v.z, v.w);
+            store4<T>(out + m * ldo + c, v.x, v.y, v.z, v.w);
         }
         return;
     }

@@ -386,7 +386,7 @@ def token_input_case(dtype, D):
           "l2.side.proj": (torch.randn(E, D, generator=g) / D ** 0.5).to(torch.bfloat16),
           "l2.side.norm": (1.0 + 0.3 * torch.randn(E, generator=g)).to(torch.bfloat16)}
     W = {k: v.double() for k, v in Wb.items()}
-    for rows in (1, 50):
+    for rows in (1, 17, 50):
         x = torch.randn(rows, E, generator=g, dtype=torch.float64) * 2.0
         toks = [int(t) for t in torch.randint(0, V, (rows,), generator=g)]
         if D == 1:
