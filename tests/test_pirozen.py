@@ -679,6 +679,33 @@ def test_generation_in_bfloat16_runs_the_recorded_step(models):
     eng.cache.check()
 
 
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_trace_replay_three_cuts(tmp_path, models, which):
+    """``bin/trace_run`` on a Pirozen folder in true 32-bit: the same requests whole, with their last 32 tokens one by one, and
+    in batches of four unequal requests one batch after another (slots and pages are used again); a cache that holds just what
+    the live requests need."""
+    from trace_tools import batched_trace, collect, run_trace, tail_trace, whole_trace
+    d, case, W = models[(which, "float32")]
+    lengths = [5, 9, 1, 17, 3, 40, 11, 70, 33, 130]
+    requests = {f"r{i}": tokens_for(case, n, 100 + i) for i, n in enumerate(lengths)}
+    want = {rid: plain_logits(case, W, toks) for rid, toks in requests.items()}
+    need = max(sum((len(requests[r]) + 63) // 64 * 64 for r in list(requests)[b:b + 4]) for b in range(0, 10, 4))
+    cuts = {}
+    for name, (steps, index), room in (("whole", whole_trace(requests), 192), ("tail", tail_trace(requests, 32), 192),
+                                       ("batched", batched_trace(requests, 4), need)):
+        run_trace(d, "float32", steps, str(tmp_path / name), max_tokens=room)
+        rows = collect(str(tmp_path / name), steps, index, case["vocab"])
+        assert len(rows) == sum(lengths), name
+        judge = Rows("float32")
+        for (rid, pos), row in rows.items():
+            judge.add(row, want[rid][pos], (name, rid, pos))
+        judge.done()
+        cuts[name] = rows
+    for key, row in cuts["whole"].items():
+        scale = np.abs(row).max()
+        assert np.abs(row - cuts["tail"][key]).max() < 2e-5 * scale and np.abs(row - cuts["batched"][key]).max() < 2e-5 * scale, key
+
+
 def test_command_line_generates(models):
     """``python -m fastgguf_b200 generate`` on a Pirozen folder: the model class comes from config.json, the tokens are
     those of Engine.generate."""
