@@ -253,24 +253,30 @@ def kernel_modules_for(spec_json, dtype_code: int) -> tuple:
         return tuple(modules + (["attn"] if dtype_code == FG_BF16 else []) + ["mix"])
     kinds = set()
     fast_attention = False
+    parts = []
     for layer in spec_json.get("layers", []):
         for role in ("mixer", "feed_forward"):
             part = layer.get(role) or {}
-            kinds.add(part.get("kind"))
-            p = part.get("params") or {}
-            if role == "mixer" and part.get("kind") == "gqa_attention" and p.get("head_dim") in (64, 128) \
-                    and p.get("v_head_dim", p.get("head_dim")) == p.get("head_dim"):
-                fast_attention = True
-            if role == "mixer" and part.get("kind") == "sink_attention" and p.get("head_dim") in (64, 128) \
-                    and p.get("v_head_dim", p.get("head_dim")) == p.get("head_dim"):
-                fast_attention = True
-            if role == "mixer" and part.get("kind") == "latent_attention" and p.get("head_dim", 0) + p.get("rot_dim", 0) in (64, 128) \
-                    and p.get("v_head_dim", 0) <= p.get("head_dim", 0) + p.get("rot_dim", 0):
-                fast_attention = True
-    builtin = {"gqa_attention", "swiglu", "retention", "mlp", "moe", "gated_linear_attention", "sink_attention", "latent_attention", None}
+            parts.append((role, part))
+            if part.get("kind") == "mixer_pair":            # two mixers side by side: both count
+                parts += [("mixer", (part.get("params") or {}).get(side) or {}) for side in ("left", "right")]
+    for role, part in parts:
+        kinds.add(part.get("kind"))
+        p = part.get("params") or {}
+        if role == "mixer" and part.get("kind") == "gqa_attention" and p.get("head_dim") in (64, 128) \
+                and p.get("v_head_dim", p.get("head_dim")) == p.get("head_dim"):
+            fast_attention = True
+        if role == "mixer" and part.get("kind") == "sink_attention" and p.get("head_dim") in (64, 128) \
+                and p.get("v_head_dim", p.get("head_dim")) == p.get("head_dim"):
+            fast_attention = True
+        if role == "mixer" and part.get("kind") == "latent_attention" and p.get("head_dim", 0) + p.get("rot_dim", 0) in (64, 128) \
+                and p.get("v_head_dim", 0) <= p.get("head_dim", 0) + p.get("rot_dim", 0):
+            fast_attention = True
+    builtin = {"gqa_attention", "swiglu", "retention", "mlp", "moe", "gated_linear_attention", "sink_attention", "latent_attention", "mixer_pair",
+               "state_space", "gated_delta", None}
     if dtype_code == FG_BF16 and (fast_attention or kinds - builtin):
         modules.append("attn")
-    if kinds & {"retention", "moe", "gated_linear_attention", "sink_attention", "latent_attention"}:
+    if kinds & {"retention", "moe", "gated_linear_attention", "sink_attention", "latent_attention", "state_space", "gated_delta"}:
         modules.append("mix")
     return tuple(modules)
 

@@ -4,5 +4,6 @@ from .llama import LlamaConfig
 from .zirivik import ZirivikConfig
 from .salulorn import SalulornConfig
 from .pirozen import PirozenConfig
+from .saluzen import SaluzenConfig
 
-__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "ZirivikConfig", "SalulornConfig", "PirozenConfig", "architecture_name", "read_config_json"]
+__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "ZirivikConfig", "SalulornConfig", "PirozenConfig", "SaluzenConfig", "architecture_name", "read_config_json"]

@@ -70,7 +70,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
     // and tables change by the step's opening copy or by decode_advance, the last kernel of a step, and this
     // pool is appended to by this kernel alone.  A caller that reorders that must launch without the overlap.
     const int pos = positions[b];
-    const int lo_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo_key = first_visible_key(pos, window);        // (window < 0: a chunked mask, see common.cuh)
     // Pages are walked by a running index: first the pages of the kept first keys that lie wholly in front of the
     // window's first page, then the window's pages; page_of gives the page of the sequence behind an index.
     const int keep = window > 0 ? rope.keep_first : 0;

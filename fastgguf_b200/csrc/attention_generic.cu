@@ -4,7 +4,8 @@
 // Reference formulas (fastgguf.c): scores s_p = scale * (q . K[p]) for p in [lo, pos]
 // (:3246, :3317), the mask is the loop range (:4782, :5030-5035), softmax with max
 // subtraction (:3147-3156), o = sum_p w_p V[p] (:3320-3323); query head h uses KV head
-// h / (H / KV) (:4781).  A window of w keeps only the last w positions (:4754-4758).
+// h / (H / KV) (:4781).  A window of w keeps only the last w positions (:4754-4758); a negative window -c is a chunked mask:
+// a row sees the keys of its own run of c positions (runs counted from the sequence's first position) up to itself.
 // keep_first > 0 adds the sequence's first keep_first positions to what a windowed row sees (they keep
 // their places; a row sees each key once).  Values may have another size (hdv) than keys (hd).
 // softcap c > 0: a score becomes c * tanh(score / c) after the scale.  sinks: one float per query head whose
@@ -44,7 +45,7 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
     int m = blockIdx.x, h = blockIdx.y;
     int kvh = h / (H / KV);
     int pos = positions[m];
-    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = first_visible_key(pos, window);
     const int n_first = min(keep_first, lo);          // kept first keys that lie in front of the window
     const int n_keys = n_first + pos - lo + 1;        // visible key v is position v (v < n_first) or lo + v - n_first
     const int *bt = block_table + (size_t)row_seq[m] * table_width;

@@ -371,8 +371,7 @@ latent_expand_kernel(const float *__restrict__ q, int ldq, const float *__restri
 template <typename T>
 __global__ void gate_slice_kernel(const T *__restrict__ x, int ldx, int stride, const float *__restrict__ gate, int ldg, T *__restrict__ out,
                                   int ldo, int H, int DV) {
-    pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait();             // (stands between two tensor-memory kernels: its successor is released when it ends, not here)
     const int m = blockIdx.x;
     for (int e = threadIdx.x; e < H * DV; e += blockDim.x) {
         const int h = e / DV, d = e - h * DV;

@@ -58,11 +58,11 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
         t_[i] = r / Gc; g_[i] = g0 + r % Gc;
         valid[i] = t_[i] < tq && g_[i] < G;
         hi[i] = valid[i] ? start + q0 + t_[i] : -1;    // the row's own position; -1 masks everything
-        lo[i] = (window > 0 && hi[i] - window + 1 > 0) ? hi[i] - window + 1 : 0;
+        lo[i] = hi[i] < 0 ? 0 : first_visible_key(hi[i], window);        // (window < 0: a chunked mask, see common.cuh)
     }
     // page range of the whole tile, and of this warp (to skip pages no row of the warp can see)
     const int tile_hi = start + q0 + tq - 1;
-    const int tile_lo = (window > 0 && start + q0 - window + 1 > 0) ? start + q0 - window + 1 : 0;
+    const int tile_lo = first_visible_key(start + q0, window);
     // Pages are walked by a running index: first the pages of the kept first keys that lie wholly in front of the
     // first page any row's window reaches, then the pages up to the tile's last row; page_of gives the sequence's page.
     const int keep = window > 0 ? keep_first : 0;

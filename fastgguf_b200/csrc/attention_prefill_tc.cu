@@ -261,13 +261,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const bool active = q0 < n_tok;                    // a CTA past the sequence's tokens only sets up and leaves
     const int tq = active ? min(TQ, n_tok - q0) : 0;
     const int tile_hi = start + q0 + tq - 1;
-    const int tile_lo = (window > 0 && start + q0 - window + 1 > 0) ? start + q0 - window + 1 : 0;
+    const int tile_lo = first_visible_key(start + q0, window);       // (window < 0: a chunked mask, see common.cuh)
     const int p_begin = tile_lo / PAGE, p_end = tile_hi / PAGE + 1;
     // Kept first keys: a row sees keys below min(keep_first, its window's start) besides its window.  The first nk
     // iterations walk the sequence's first pages for them (each row masks what its window shows anyway, so a page that
     // both walks reach is counted once), the others the window's pages as before.
     const int keep = window > 0 ? keep_first : 0;
-    const int tile_lo_max = (window > 0 && tile_hi - window + 1 > 0) ? tile_hi - window + 1 : 0;       // the last row's window start
+    const int tile_lo_max = tile_hi < 0 ? 0 : first_visible_key(tile_hi, window);       // the last row's window start
     const int nk = active ? ((min(keep, tile_lo_max) + PAGE - 1) / PAGE + NPG - 1) / NPG : 0;
     const int n_iter = active ? nk + (p_end - p_begin + NPG - 1) / NPG : 0;
     auto first_page_of = [&](int j) { return j < nk ? NPG * j : p_begin + NPG * (j - nk); };
@@ -284,7 +284,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         // neither asks for the masked loop nor, with a maximum that stays at minus infinity, for the second pass in
         // every iteration of its warp (group sizes that do not divide 128 leave such rows in every tile).
         hi = valid ? start + q0 + t_row : INT_MAX;
-        lo = !valid ? INT_MIN : (window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
+        lo = !valid ? INT_MIN : first_visible_key(hi, window);
         const bf16 *src = q + (size_t)(row0 + q0 + t_row) * ldq + (size_t)(kvh * G + g_row) * HD;
 #pragma unroll
         for (int c = (warp < 6 ? 0 : HD / 8); c < HD / 8; c++) {       // (PP: the first set brings the tile)

@@ -33,11 +33,11 @@ MODULES = {
     "attn": ["attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu"],
     # mixers beyond plain attention: retention and gated linear attention (a state per sequence), what stands between an
     # attention mixer's projections and its scores (convolution, norms, adjacent-pair rotation, latents), and the experts
-    "mix": ["retention.cu", "experts.cu", "gla.cu", "attention_prep.cu", "attention_latent.cu"],
+    "mix": ["retention.cu", "experts.cu", "gla.cu", "attention_prep.cu", "attention_latent.cu", "recurrence.cu"],
     # the C++ host: configuration, weights, cache, step function, generation loop, C interface; it opens the
     # kernel libraries above by name when a model first needs them
-    "engine": ["host/api.cpp", "host/cache.cpp", "host/config.cpp", "host/config_zirivik.cpp", "host/config_salulorn.cpp", "host/config_pirozen.cpp", "host/device.cpp", "host/model.cpp", "host/parts.cpp",
-               "host/parts_recurrent.cpp", "host/parts_attention.cpp", "host/parts_experts.cpp", "host/runner.cpp", "host/safetensors.cpp", "host/host_kernels.cu"],
+    "engine": ["host/api.cpp", "host/cache.cpp", "host/config.cpp", "host/config_zirivik.cpp", "host/config_salulorn.cpp", "host/config_pirozen.cpp", "host/config_saluzen.cpp", "host/device.cpp", "host/model.cpp", "host/parts.cpp",
+               "host/parts_recurrent.cpp", "host/parts_attention.cpp", "host/parts_experts.cpp", "host/parts_pair.cpp", "host/runner.cpp", "host/safetensors.cpp", "host/host_kernels.cu"],
 }
 LINK_FLAGS = {"engine": ["-ldl"]}
 HEADERS = ["common.cuh"]

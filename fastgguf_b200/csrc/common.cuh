@@ -76,6 +76,14 @@ __device__ __forceinline__ float block_max(float v, float *scratch) {
 
 #define FG_LAUNCH_CHECK() ((int)cudaGetLastError())
 
+// The first key a row at position pos sees.  window == 0: the sequence's first; window > 0: the last `window` positions, the
+// row's own included; window < 0: the start of the row's run of -window positions, runs counted from the sequence's first
+// position (a chunked mask).  It never falls as pos grows, which is what the tiled kernels' page ranges rest on.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    return window < 0 ? pos - pos % (-window) : 0;
+}
+
 // One lane of a converged warp (elect.sync).  A loop that the whole warp walks, with only the
 // asynchronous instructions (tcgen05.mma, tcgen05.commit, TMA copies) under this predicate, keeps its
 // counters, barrier addresses and descriptors in the uniform datapath; the same loop inside

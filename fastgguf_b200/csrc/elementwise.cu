@@ -361,6 +361,41 @@ extern "C" int fg_norm_add_norm(const float *t, const float *w_post, float *x, c
 #undef NAN_LAUNCH
 }
 
+// ------------------------------------------------------------------ two mixers side by side
+// out (+)= scale_a * f_a(a) + scale_b * f_b(b) over float32 rows [M, E], f(t) = t / sqrt(mean(t^2) + eps) * w where a weight is
+// given and t itself where it is not.  One block a row; statistics and the sum are 32-bit, fixed reduction order.
+__global__ void pair_combine_kernel(const float *__restrict__ a, const float *__restrict__ b, const float *__restrict__ w_a,
+                                    const float *__restrict__ w_b, float scale_a, float scale_b, float eps, float *__restrict__ out,
+                                    int E, int accumulate) {
+    __shared__ float scratch[32];
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * E;
+    float inv_a = 1.f, inv_b = 1.f;
+    if (w_a) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < E; i += blockDim.x) { const float v = a[base + i]; ss = fmaf(v, v, ss); }
+        inv_a = 1.0f / sqrtf(block_sum(ss, scratch) / (float)E + eps);
+    }
+    if (w_b) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < E; i += blockDim.x) { const float v = b[base + i]; ss = fmaf(v, v, ss); }
+        inv_b = 1.0f / sqrtf(block_sum(ss, scratch) / (float)E + eps);
+    }
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        const float ta = w_a ? a[base + i] * inv_a * w_a[i] : a[base + i], tb = w_b ? b[base + i] * inv_b * w_b[i] : b[base + i];
+        const float v = fmaf(scale_a, ta, scale_b * tb);
+        out[base + i] = accumulate ? out[base + i] + v : v;
+    }
+}
+
+extern "C" int fg_pair_combine(const float *a, const float *b, const float *w_a, const float *w_b, float scale_a, float scale_b,
+                               float eps, float *out, int M, int E, int accumulate, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (E <= 0) return FG_ERR_BAD_SIZE;
+    const int threads = E >= 2048 ? 256 : 128;
+    return fg_launch_in_order(pair_combine_kernel, dim3(M), dim3(threads), 0, stream, a, b, w_a, w_b, scale_a, scale_b, eps, out, E, accumulate);
+}
+
 // ------------------------------------------------------------------ activations in place
 // kind 0: relu(z)^2.  In f32; the result is stored in the buffer's dtype.
 template <typename T>

@@ -43,6 +43,9 @@ int fg_softcap(float *logits, int R, int V, int ld, float cap, cudaStream_t stre
 int fg_concat2(const float *a, int lda, const float *b, int ldb, void *out, int out_dtype, int ldo, int M, int E,
                cudaStream_t stream);
 int fg_silu_mul(const void *gu, void *out, int dtype, int M, int F, cudaStream_t stream);
+/* out (+)= scale_a * f_a(a) + scale_b * f_b(b) over float32 rows [M, E]; f(t) = t / rms(t) * w with a weight, t itself without */
+int fg_pair_combine(const float *a, const float *b, const float *w_a, const float *w_b, float scale_a, float scale_b, float eps,
+                    float *out, int M, int E, int accumulate, cudaStream_t stream);
 /* out_a = x / rms(x) * w_a and out_b = x / rms(x) * w_b of the same float32 rows, one pass */
 int fg_rmsnorm_pair(const float *x, const float *w_a, const float *w_b, void *out_a, void *out_b, int out_dtype, int R, int E,
                     float eps_a, float eps_b, cudaStream_t stream);
@@ -97,6 +100,29 @@ int fg_gla_chunked_ok(int dk, int dv);
 int fg_gla_chunked(const float *proj, int ld, const float *z, int ldz, const float *z_bias, const float *norm_w, void *out,
                    int out_dtype, int ldo, const int *cu_rows, const int *slots, float *state, int *plan, float *U, float *D,
                    int n_seq, int n_chunks, int H, int dk, int dv, float tau, float q_scale, float eps, cudaStream_t stream);
+/* recurrences with one decay a head and token (recurrence.cu): S <- a S; u = b (v - [delta] S^T k); S <- S + k u^T;
+   o = S^T q + skip v.  q, k [M, Hq, d], v [M, H, dv], decay and step [M, H], out [M, H * dv], all float32; a sequence's state
+   row (state_stride floats apart) holds fg_decay_recurrence_state_floats(H, d, dv) floats in the kernel's own layout */
+int fg_decay_recurrence_lanes(int d);
+long long fg_decay_recurrence_state_floats(int H, int d, int dv);
+int fg_decay_recurrence(const float *q, int ldq, const float *k, int ldk, const float *v, int ldv, const float *decay,
+                        const float *step, const float *skip, float *out, int ldo, const int *cu_rows, const int *slots,
+                        float *state, long long state_stride, int n_seq, int H, int Hq, int d, int dv, int delta,
+                        cudaStream_t stream);
+/* out = silu(bias + causal convolution over time of each channel), weights [C, taps]; a sequence's last taps - 1 inputs live in
+   its state row [taps - 1, C]; fg_conv1d_state brings them up to date after the step's rows have been read */
+int fg_conv1d_silu(const float *in, int ld, const float *w, const float *bias, int taps, const float *state, long long state_stride,
+                   const int *row_seq, const int *cu_rows, const int *slots, float *out, int ldo, int M, int C, cudaStream_t stream);
+int fg_conv1d_state(const float *in, int ld, int taps, float *state, long long state_stride, const int *cu_rows, const int *slots,
+                    int n_seq, int C, cudaStream_t stream);
+/* mode 0: step = softplus(a_raw + dt_bias), decay = exp(-exp(A_log) step); mode 1: decay = exp(-exp(A_log) softplus(a_raw +
+   dt_bias)), step = sigmoid(b_raw); decay and step [M, H] */
+int fg_decay_gates(const float *a_raw, int lda, const float *b_raw, int ldb, const float *A_log, const float *dt_bias, int mode,
+                   float *decay, float *step, int M, int H, cudaStream_t stream);
+int fg_unit_heads(float *x, int ld, int n_heads, int d, float eps, float scale, int M, cudaStream_t stream);
+/* gate_first: t = y silu(g), out = t / rms(t) * w over groups of `group` channels; else out = y / rms(y) * w[c % w_period] * silu(g) */
+int fg_gated_group_norm(const float *y, int ldy, const float *g, int ldg, const float *w, int w_period, void *out, int out_dtype,
+                        int ldo, int M, int C, int group, float eps, int gate_first, cudaStream_t stream);
 /* between an attention mixer's projections and its attention kernel (attention_prep.cu) */
 int fg_qkv_prepare(const float *proj, int ld, const float *bias, const float *conv_w, int taps, const float *conv_state,
                    const float *qn_w, const float *kn_w, float eps, const float *cos_t, const float *sin_t, int tbl_half,

@@ -157,9 +157,11 @@ static std::mutex g_registry_mutex;
 std::unique_ptr<ModelConfig> zirivik_config_from_json(const Json &d);        // config_zirivik.cpp
 std::unique_ptr<ModelConfig> salulorn_config_from_json(const Json &d);       // config_salulorn.cpp
 std::unique_ptr<ModelConfig> pirozen_config_from_json(const Json &d);        // config_pirozen.cpp
+std::unique_ptr<ModelConfig> saluzen_config_from_json(const Json &d);        // config_saluzen.cpp
 static std::map<std::string, ConfigReader> &registry() {
     static std::map<std::string, ConfigReader> r = {{"LlamaForCausalLM", &LlamaConfig::from_json}, {"Zirivik", &zirivik_config_from_json},
-                                                    {"Salulorn", &salulorn_config_from_json}, {"Pirozen", &pirozen_config_from_json}};
+                                                    {"Salulorn", &salulorn_config_from_json}, {"Pirozen", &pirozen_config_from_json},
+                                                    {"Saluzen", &saluzen_config_from_json}};
     return r;
 }
 

@@ -334,6 +334,7 @@ void DecoderModel::make_cache(int64_t max_tokens, int n_slots, int max_seq_len, 
         l.write_cache = run.cache_from < 0;
         l.state = state->of((int)i);
         l.state_bytes = state->bytes_of((int)i);
+        l.state_stride = l.state_bytes;
         l.n_slots = n_slots;
         l.page_size = page_size;
         l.cache_dtype = runtime.dtype;

@@ -1279,6 +1279,7 @@ static std::map<std::string, PartFactory> &factories(int role) {
         add_recurrent_kinds(r[FG_ROLE_MIXER]);
         add_attention_kinds(r[FG_ROLE_MIXER]);
         add_expert_kinds(r[FG_ROLE_FEED_FORWARD]);
+        add_pair_kinds(r[FG_ROLE_MIXER]);
     }
     if (role < 0 || role > 8) fail(FG_E_USAGE, format("role %d does not exist", role));
     return r[role];

@@ -77,6 +77,7 @@ struct LayerIO {
     bool write_cache = true;          // false: the cache belongs to an earlier entry
     void *state = nullptr;
     int64_t state_bytes = 0;
+    int64_t state_stride = 0;         // bytes between two slots' rows (a mixer inside a pair owns only a part of a row)
     int n_slots = 0;
     fg_layer_io view() const;
 };
@@ -128,6 +129,8 @@ class Mixer : public Part {
 public:
     virtual bool cache_request(CacheRequest *out) const { (void)out; return false; }
     virtual int64_t state_bytes() const { return 0; }
+    // true: the mixer reads LayerIO::state_stride, so its state may be a part of a wider row
+    virtual bool strided_state() const { return false; }
     virtual bool supports_deferred_norm() const { return false; }
     virtual bool can_overwrite() const { return false; }      // honours Runtime::overwrite
     // adds its output into residual ([M, E] f32).  xn: normalised rows, or (deferred) a started norm;
@@ -217,6 +220,7 @@ void register_external_part(int role, const std::string &kind, const fg_part_vta
 void add_recurrent_kinds(std::map<std::string, PartFactory> &mixers);
 void add_attention_kinds(std::map<std::string, PartFactory> &mixers);
 void add_expert_kinds(std::map<std::string, PartFactory> &feed_forwards);
+void add_pair_kinds(std::map<std::string, PartFactory> &mixers);
 // the built-in gated feed-forward {hidden_size, d_ff} for parts that hold one inside (a shared expert)
 std::unique_ptr<FeedForward> make_swiglu(const Json &params);
 

@@ -11,9 +11,13 @@
 //     score = scale * (q . k), then softcap * tanh(score / softcap)
 //     a row sees itself and the window - 1 keys before it
 //     the softmax's denominator also holds exp(sink_h), a learned number per head
+//     ("chunk": c instead of a window: a row sees the keys of its own run of c positions, runs counted from the sequence's
+//     first position, up to itself; "unit_sink": true instead of learned sinks: a sink of score 0, so that the softmax's
+//     denominator is one plus the sum)
 //   and, as further options: the q/k norm per head with one weight vector [head_dim] for all heads of q and one for all heads
 //   of k ("qk_norm": "head"); rotated pairs (i, i + rotary_dim / 2) when the position part's layout is "halves"; a gate per
-//   head on the heads' outputs, o_h <- o_h * sigmoid(W_g h)_h with W_g [heads, hidden] ("gate": "head"); a bias on the output
+//   head on the heads' outputs, o_h <- o_h * sigmoid(W_g h)_h with W_g [heads, hidden] ("gate": "head"), or a gate per number,
+//   o <- o * sigmoid(W_g h) with W_g [heads * v_head_dim, hidden] ("gate": "full"); a bias on the output
 //   projection ("o_bias": true), stored as one more column of the output matrix that meets a column of ones, so the
 //   projection's own pass adds it.
 //
@@ -24,6 +28,9 @@
 // rotated part (in the key pool) only.  The key map is folded into the query, q_abs[h] = W_uk[h]^T q_plain[h], so that a score
 // is q_abs . c + q_rot . k_rot, and the value map is applied to the attention's output over the latents,
 // o[h] = W_uv[h] (sum_j p_j c_j): the same sums in another order, for prompts, portions and single tokens alike.
+// "shared_kv": true: the layer has no W_dkv; its schedule entry reads the latents and rotated key parts that an earlier latent
+// attention layer of the same kv_rank, rot_dim and rotation keeps (the entry's cache_from), with W_uk, W_uv, queries and
+// everything else of its own.
 #include <algorithm>
 #include <cmath>
 
@@ -48,19 +55,25 @@ public:
         if (H_ % KV_) fail(FG_E_CONFIG, format("sink_attention: %d heads are not a multiple of %d KV heads", H_, KV_));
         scale_ = (float)param_float(p, "scale", 1.0 / std::sqrt((double)hd_), me);
         window_ = (int)param_int(p, "window", 0, me);
+        chunk_ = (int)param_int(p, "chunk", 0, me);
         softcap_ = (float)param_float(p, "softcap", 0.0, me);
         taps_ = (int)param_int(p, "conv_taps", 0, me);
         eps_ = (float)param_float(p, "eps", 1e-6, me);
         bias_ = flag(p, "bias");
         sink_ = flag(p, "sink");
+        unit_sink_ = flag(p, "unit_sink");
+        if (sink_ && unit_sink_) fail(FG_E_CONFIG, "sink_attention: learned sinks and a unit sink exclude one another");
+        if (chunk_ < 0 || (chunk_ > 0 && window_ > 0)) fail(FG_E_CONFIG, "sink_attention: 'chunk' cannot be negative or stand beside a window");
         const Json &qn = p.get("qk_norm");
         if (!qn.is_null() && !(qn.is_string() && (qn.as_string() == "whole" || qn.as_string() == "head")))
             fail(FG_E_CONFIG, "sink_attention: qk_norm " + qn.dump() + " is not known (known: whole, head)");
         qk_norm_ = !qn.is_null();
         norm_per_head_ = qk_norm_ && qn.as_string() == "head";
         const Json &gt = p.get("gate");
-        if (!gt.is_null() && !(gt.is_string() && gt.as_string() == "head")) fail(FG_E_CONFIG, "sink_attention: gate " + gt.dump() + " is not known (known: head)");
+        if (!gt.is_null() && !(gt.is_string() && (gt.as_string() == "head" || gt.as_string() == "full")))
+            fail(FG_E_CONFIG, "sink_attention: gate " + gt.dump() + " is not known (known: head, full)");
         gate_ = !gt.is_null();
+        gate_full_ = gate_ && gt.as_string() == "full";
         o_bias_ = flag(p, "o_bias");
         // columns behind the heads' outputs that carry the output bias: as many as keep a row a multiple of 8 numbers
         pad_ = o_bias_ ? 8 - (int)(((int64_t)H_ * hdv_) % 8) : 0;
@@ -91,11 +104,12 @@ public:
             d.push_back({"k_norm.weight", {norm_per_head_ ? (int64_t)hd_ : K}, false, 1, 0.01f});
         }
         if (sink_) d.push_back({"sinks", {(int64_t)H_}, false, 0, 1.0f});
-        if (gate_) d.push_back({"g_proj.weight", {(int64_t)H_, E_}});
+        if (gate_) d.push_back({"g_proj.weight", {gate_full_ ? (int64_t)H_ * hdv_ : (int64_t)H_, E_}});
         if (o_bias_) d.push_back({"o_proj.bias", {(int64_t)E_}});
         return d;
     }
     bool cache_request(CacheRequest *out) const override {
+        // (a chunked mask keeps every page: a sequence's pages are given back when it ends)
         out->n_kv_heads = KV_; out->head_dim = hd_; out->window = window_; out->v_head_dim = hdv_; out->keep_first = 0;
         return true;
     }
@@ -143,6 +157,11 @@ public:
         if (taps_ > 0) conv_w_ = three("q_conv.weight", "k_conv.weight", "v_conv.weight", taps_);
         if (qk_norm_) { qn_w_ = as_f32(tensor_of(tensors, "q_norm.weight"), rt.stream); kn_w_ = as_f32(tensor_of(tensors, "k_norm.weight"), rt.stream); }
         if (sink_) sinks_w_ = as_f32(tensor_of(tensors, "sinks"), rt.stream);
+        if (unit_sink_) {
+            sinks_w_ = make_weight(1, H_, FG_F32, "unit sinks");
+            FG_CUDA(cudaMemsetAsync(sinks_w_.t.data, 0, (size_t)H_ * sizeof(float), rt.stream));
+            FG_CUDA(cudaStreamSynchronize(rt.stream));
+        }
     }
     void prepare(Runtime &rt, int max_positions) override { if (position_) position_->prepare(rt, max_positions); }
     DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *deferred, const Batch &b, const LayerIO &io, Tensor &residual,
@@ -165,7 +184,8 @@ public:
                       (int)channels(), rt.stream);
         // (with an output bias the rows are wider than the heads' outputs: the columns behind them carry the ones)
         Tensor attn = rt.arena->matrix(M, (int64_t)H_ * hdv_ + pad_, rt.dtype);
-        const float *sinks = sink_ ? sinks_w_.t.ptr<float>() : nullptr;
+        const float *sinks = (sink_ || unit_sink_) ? sinks_w_.t.ptr<float>() : nullptr;
+        const int mask = chunk_ > 0 ? -chunk_ : window_;     // what the kernels call a window: negative for a chunked mask
         // bfloat16 with head size 64 / 128 for keys and values alike: the tensor-core kernels (a decode step: mma.sync with the
         // pages split over a cluster; portions: tcgen05 tiles of 128 rows, or mma.sync tiles of 64 for a few rows)
         const bool fast = !rt.plain_kernels && rt.dtype == FG_BF16 && io.cache_dtype == FG_BF16 && (hd_ == 64 || hd_ == 128) && hdv_ == hd_ &&
@@ -178,29 +198,33 @@ public:
                 part_ml = (float *)rt.arena->alloc((size_t)b.n_seq * H_ * n_splits * 2 * sizeof(float));
             }
             FG_LAUNCH("attn", fg_attention_decode_ext, q.data, (int)q.ld, attn.data, (int)attn.ld, b.positions, table, b.table_width, io.k_pool,
-                      io.v_pool, b.n_seq, H_, KV_, hd_, io.page_size, scale_, window_, 0, n_splits, part_o, part_ml, softcap_, sinks, rt.stream);
+                      io.v_pool, b.n_seq, H_, KV_, hd_, io.page_size, scale_, mask, 0, n_splits, part_o, part_ml, softcap_, sinks, rt.stream);
         } else if (fast && b.max_new * (H_ / KV_) >= 64) {
             FG_LAUNCH("attn", fg_attention_prefill_tc_ext, q.data, (int)q.ld, attn.data, (int)attn.ld, b.cu_rows, b.seq_start, table, b.table_width,
-                      io.k_pool, io.v_pool, io.n_pages, b.n_seq, b.max_new, H_, KV_, hd_, io.page_size, scale_, window_, 0, softcap_, sinks, rt.stream);
+                      io.k_pool, io.v_pool, io.n_pages, b.n_seq, b.max_new, H_, KV_, hd_, io.page_size, scale_, mask, 0, softcap_, sinks, rt.stream);
         } else if (fast) {
             FG_LAUNCH("attn", fg_attention_prefill_ext, q.data, (int)q.ld, attn.data, (int)attn.ld, b.cu_rows, b.seq_start, table, b.table_width,
-                      io.k_pool, io.v_pool, b.n_seq, b.max_new, H_, KV_, hd_, io.page_size, scale_, window_, 0, softcap_, sinks, rt.stream);
+                      io.k_pool, io.v_pool, b.n_seq, b.max_new, H_, KV_, hd_, io.page_size, scale_, mask, 0, softcap_, sinks, rt.stream);
         } else {
             FG_LAUNCH("core", fg_attention_generic_ext, q.data, (int)q.ld, attn.data, (int)attn.ld, rt.dtype, b.positions, b.row_seq, table,
-                      b.table_width, io.k_pool, io.v_pool, M, H_, KV_, hd_, hdv_, io.page_size, scale_, window_, 0, softcap_, sinks, 0, rt.stream);
+                      b.table_width, io.k_pool, io.v_pool, M, H_, KV_, hd_, hdv_, io.page_size, scale_, mask, 0, softcap_, sinks, 0, rt.stream);
         }
-        if (gate_ || pad_ > 0)
-            FG_LAUNCH("mix", fg_head_gate, attn.data, (int)attn.ld, attn.dtype, gate_ ? proj.ptr<float>() + channels() : nullptr, (int)proj.ld, M, H_, hdv_,
-                      pad_, rt.stream);
+        if (gate_full_)           // in place: a thread reads and writes its own number
+            FG_LAUNCH("mix", fg_gate_slice, attn.data, (int)attn.ld, hdv_, proj.ptr<float>() + channels(), (int)proj.ld, attn.data, (int)attn.ld, attn.dtype, M,
+                      H_, hdv_, rt.stream);
+        if ((gate_ && !gate_full_) || pad_ > 0)
+            FG_LAUNCH("mix", fg_head_gate, attn.data, (int)attn.ld, attn.dtype, (gate_ && !gate_full_) ? proj.ptr<float>() + channels() : nullptr, (int)proj.ld,
+                      M, H_, hdv_, pad_, rt.stream);
         DeferredNorm started;
         o_.forward(rt, attn, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
         return started;
     }
 
 private:
-    int E_ = 0, H_ = 0, KV_ = 0, hd_ = 0, hdv_ = 0, window_ = 0, taps_ = 0, rot_dims_ = 0, pad_ = 0;
+    int E_ = 0, H_ = 0, KV_ = 0, hd_ = 0, hdv_ = 0, window_ = 0, chunk_ = 0, taps_ = 0, rot_dims_ = 0, pad_ = 0;
     float scale_ = 1.f, softcap_ = 0.f, eps_ = 1e-6f;
-    bool bias_ = false, sink_ = false, qk_norm_ = false, norm_per_head_ = false, rot_halves_ = false, gate_ = false, o_bias_ = false;
+    bool bias_ = false, sink_ = false, unit_sink_ = false, qk_norm_ = false, norm_per_head_ = false, rot_halves_ = false, gate_ = false, gate_full_ = false,
+         o_bias_ = false;
     PositionEncoding *position_ = nullptr;
     Linear qkv_, o_;
     Weight bias_w_, conv_w_, qn_w_, kn_w_, sinks_w_;
@@ -224,6 +248,7 @@ public:
         eps_ = (float)param_float(p, "eps", 1e-6, me);
         sink_ = flag(p, "sink");
         gate_ = flag(p, "gate");
+        shared_kv_ = flag(p, "shared_kv");
         const Json &pos = p.get("position");
         position_ = pos.is_null() ? nullptr : dynamic_cast<PositionEncoding *>(ctx.nested(FG_ROLE_POSITION, pos));
         if (!position_) fail(FG_E_CONFIG, "latent_attention: 'position' must be a position encoding for the rotated part");
@@ -233,8 +258,11 @@ public:
     std::vector<TensorDecl> tensor_decls() const override {
         const int64_t HV = (int64_t)H_ * dv_;
         std::vector<TensorDecl> d = {{"q_down.weight", {qr_, E_}}, {"q_down_norm.weight", {qr_}, false, 1, 0.01f}, {"q_up.weight", {(int64_t)H_ * (d_ + dr_), qr_}},
-                                     {"kv_down.weight", {(int64_t)r_ + dr_, E_}}, {"kv_down_norm.weight", {r_}, false, 1, 0.01f},
                                      {"k_up.weight", {(int64_t)H_ * d_, r_}}, {"v_up.weight", {HV, r_}}, {"o_proj.weight", {E_, HV}}};
+        if (!shared_kv_) {
+            d.push_back({"kv_down.weight", {(int64_t)r_ + dr_, E_}});
+            d.push_back({"kv_down_norm.weight", {r_}, false, 1, 0.01f});
+        }
         if (gate_) d.push_back({"g_proj.weight", {HV, E_}});
         if (sink_) d.push_back({"sinks", {(int64_t)H_}, false, 0, 1.0f});
         return d;
@@ -247,9 +275,10 @@ public:
     bool supports_deferred_norm() const override { return true; }
     bool can_overwrite() const override { return true; }
     void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
-        const Weight &dq = tensor_of(tensors, "q_down.weight"), &dkv = tensor_of(tensors, "kv_down.weight");
-        std::vector<Weight> parts = {dq, dkv};
-        bool same = dq.t.dtype == dkv.t.dtype;
+        const Weight &dq = tensor_of(tensors, "q_down.weight");
+        std::vector<Weight> parts = {dq};
+        bool same = true;
+        if (!shared_kv_) { parts.push_back(tensor_of(tensors, "kv_down.weight")); same = parts.back().t.dtype == dq.t.dtype; }
         if (gate_) { parts.push_back(tensor_of(tensors, "g_proj.weight")); same = same && parts.back().t.dtype == dq.t.dtype; }
         down_ = Linear(concat_rows(parts, same ? dq.t.dtype : FG_F32, rt.stream));
         q_up_ = Linear(tensor_of(tensors, "q_up.weight"));
@@ -259,13 +288,14 @@ public:
         v_lin_ = Linear(v_up_);
         o_ = Linear(tensor_of(tensors, "o_proj.weight"));
         qn_w_ = as_f32(tensor_of(tensors, "q_down_norm.weight"), rt.stream);
-        kvn_w_ = as_f32(tensor_of(tensors, "kv_down_norm.weight"), rt.stream);
+        if (!shared_kv_) kvn_w_ = as_f32(tensor_of(tensors, "kv_down_norm.weight"), rt.stream);
         if (sink_) sinks_w_ = as_f32(tensor_of(tensors, "sinks"), rt.stream);
     }
     void prepare(Runtime &rt, int max_positions) override { position_->prepare(rt, max_positions); }
     DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *deferred, const Batch &b, const LayerIO &io, Tensor &residual,
                          Norm *emit_norm) override {
-        if (io.group < 0 || !io.k_pool || !io.write_cache) fail(FG_E_INTERNAL, "latent_attention: the schedule entry has no cache of its own");
+        if (io.group < 0 || !io.k_pool || (!shared_kv_ && !io.write_cache)) fail(FG_E_INTERNAL, "latent_attention: the schedule entry has no cache of its own");
+        if (shared_kv_ && io.write_cache) fail(FG_E_CONFIG, "latent_attention: a layer without a key/value latent of its own must read an earlier entry's cache");
         const int *table = b.block_tables.at((size_t)io.group);
         const float *cos_t = position_->cos_table(), *sin_t = position_->sin_table();
         // [q latent | kv latent and rotated key part | gate], float32: norms and the rotation read them
@@ -274,15 +304,16 @@ public:
         Tensor cq = rt.arena->matrix(M, qr_, rt.dtype);
         FG_LAUNCH("mix", fg_rmsnorm_strided, down.ptr<float>(), (int)down.ld, qn_w_.t.ptr<float>(), cq.data, cq.dtype, (int)cq.ld, M, qr_, eps_, rt.stream);
         Tensor q = q_up_.forward(rt, cq, nullptr, Tensor(), FG_F32, false, nullptr, nullptr);
-        FG_LAUNCH("mix", fg_latent_append, down.ptr<float>() + qr_, (int)down.ld, kvn_w_.t.ptr<float>(), eps_, cos_t, sin_t, dr_ / 2, b.positions,
-                  b.row_seq, table, b.table_width, io.k_pool, io.v_pool, rt.dtype, M, r_, dr_, io.page_size, rt.stream);
+        if (!shared_kv_)
+            FG_LAUNCH("mix", fg_latent_append, down.ptr<float>() + qr_, (int)down.ld, kvn_w_.t.ptr<float>(), eps_, cos_t, sin_t, dr_ / 2, b.positions,
+                      b.row_seq, table, b.table_width, io.k_pool, io.v_pool, rt.dtype, M, r_, dr_, io.page_size, rt.stream);
         Tensor o = rt.arena->matrix(M, (int64_t)H_ * dv_, rt.dtype);
-        const float *gate = gate_ ? down.ptr<float>() + qr_ + r_ + dr_ : nullptr;
+        const float *gate = gate_ ? down.ptr<float>() + qr_ + (shared_kv_ ? 0 : r_ + dr_) : nullptr;
         const float *sinks = sink_ ? sinks_w_.t.ptr<float>() : nullptr;
         const int HQ = d_ + dr_;
         // A step of whole prompts in bfloat16 whose head sizes the tensor-core kernels take: ordinary multi-head attention over
         // keys and values expanded for the step's tokens (nothing older is in the cache), in pools of the step's own.
-        bool whole_prompts = !b.single_token && !b.host_seq_start.empty() && !rt.plain_kernels && rt.dtype == FG_BF16 && (HQ == 64 || HQ == 128) &&
+        bool whole_prompts = !shared_kv_ && !b.single_token && !b.host_seq_start.empty() && !rt.plain_kernels && rt.dtype == FG_BF16 && (HQ == 64 || HQ == 128) &&
                              dv_ <= HQ && io.page_size == 64 && b.n_seq <= 1024 && k_up_.t.dtype == FG_BF16 && v_up_.t.dtype == FG_BF16;
         for (size_t s = 0; whole_prompts && s < b.host_seq_start.size(); s++) whole_prompts = b.host_seq_start[s] == 0;
         if (whole_prompts) {
@@ -351,7 +382,7 @@ public:
 private:
     int E_ = 0, H_ = 0, d_ = 0, dr_ = 0, dv_ = 0, r_ = 0, qr_ = 0;
     float scale_ = 1.f, eps_ = 1e-6f;
-    bool sink_ = false, gate_ = false;
+    bool sink_ = false, gate_ = false, shared_kv_ = false;
     PositionEncoding *position_ = nullptr;
     Linear down_, q_up_, o_, k_lin_, v_lin_;
     Weight k_up_, v_up_, qn_w_, kvn_w_, sinks_w_;

@@ -1,4 +1,6 @@
-// Mixers that carry a state of fixed size from token to token instead of keys and values per position.
+// Mixers that carry a state of fixed size from token to token instead of keys and values per position: retention, gated
+// linear attention, and - behind a short convolution, with one decay per head and token - the state-space form and the gated
+// delta rule.
 //
 // "retention": linear attention with a fixed decay per head and neither softmax nor denominator.  With the layer's
 // normalised input h, per head (q, k of size head_dim, v of size v_head_dim):
@@ -219,9 +221,213 @@ private:
     Weight bias_, norm_;
 };
 
+// What the two mixers below share: a short causal convolution with SiLU in front of the recurrence, whose last taps - 1 inputs
+// are the first part of the mixer's state row, and the recurrence of recurrence.cu behind it, whose state is the second part.
+static Weight f32_rows(const std::vector<Weight> &parts, cudaStream_t s) { return concat_rows(parts, FG_F32, s); }
+// Floats of a sequence's recurrence state, as recurrence.cu lays it out: a column of a head's [d, dv] state is shared by R
+// lanes, the smallest power of two that leaves a lane at most 16 rows, and rows are padded to a multiple of R.  (Computed
+// here so that sizing a cache needs no kernel library; load() checks it against the library's own answer.)
+static int64_t recurrence_state_floats(int H, int d, int dv, const char *who) {
+    int R = 1;
+    while (R < 32 && (d + R - 1) / R > 16) R *= 2;
+    if ((d + R - 1) / R > 16) fail(FG_E_CONFIG, std::string(who) + ": the state of a head exceeds what the kernel takes");
+    return (int64_t)H * ((d + R - 1) / R) * dv * R;
+}
+static void check_state_floats(int H, int d, int dv, const char *who) {
+    if (FG_KERNEL("mix", fg_decay_recurrence_state_floats)(H, d, dv) != recurrence_state_floats(H, d, dv, who))
+        fail(FG_E_INTERNAL, std::string(who) + ": host and kernel library disagree on the size of a state row");
+}
+
+// "state_space": the state-space form with a scalar decay per head and token ("duality").  With the normalised input h,
+// inner = n_heads * v_head_dim, N = state_size and G = n_groups (head h uses group h / (n_heads / G)):
+//     W_in h = [z: inner | x: inner | B: G N | C: G N | dt: n_heads]
+//     (x, B, C) <- silu(causal convolution over time per channel + bias)          weights [inner + 2 G N, taps]
+//     dt <- softplus(dt + dt_bias);  S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T (S: [N, v_head_dim]);  y_t = S_t^T C_t + D x_t
+//     y <- y * silu(z), then an RMS norm in norm_groups equal parts of the inner channels, times a weight [inner]; output W_o y
+// Projections leave their contraction as float32; convolution, decays, steps, state, gate and norm are float32 on the FMA units
+// in every engine dtype; only the normalised y takes the engine's dtype, as the output projection's input.
+class StateSpaceMixer : public Mixer {
+public:
+    StateSpaceMixer(const Json &p, BuildContext &) {
+        const char *me = "state_space";
+        E_ = (int)param_int(p, "hidden_size", me);
+        H_ = (int)param_int(p, "n_heads", me);
+        dv_ = (int)param_int(p, "v_head_dim", me);
+        N_ = (int)param_int(p, "state_size", me);
+        G_ = (int)param_int(p, "n_groups", 1, me);
+        taps_ = (int)param_int(p, "conv_taps", 1, me);
+        norm_groups_ = (int)param_int(p, "norm_groups", 1, me);
+        eps_ = (float)param_float(p, "eps", me);
+        if (E_ <= 0 || H_ <= 0 || dv_ <= 0 || N_ <= 0 || G_ <= 0 || taps_ <= 0 || norm_groups_ <= 0) fail(FG_E_CONFIG, "state_space: sizes must be positive");
+        if (H_ % G_) fail(FG_E_CONFIG, format("state_space: %d heads are not a multiple of %d groups", H_, G_));
+        if ((H_ * dv_) % norm_groups_) fail(FG_E_CONFIG, format("state_space: %d inner channels do not split into %d norm groups", H_ * dv_, norm_groups_));
+        if (N_ > 512) fail(FG_E_CONFIG, format("state_space: state_size %d exceeds 512, the largest the kernel takes", N_));
+        if (!(eps_ > 0.f)) fail(FG_E_CONFIG, "state_space: eps must be positive");
+    }
+    int64_t inner() const { return (int64_t)H_ * dv_; }
+    int64_t conv_channels() const { return inner() + (int64_t)2 * G_ * N_; }
+    int64_t conv_floats() const { return (int64_t)(taps_ - 1) * conv_channels(); }
+    std::vector<TensorDecl> tensor_decls() const override {
+        const int64_t I = inner(), C = conv_channels();
+        return {{"in_proj.weight", {2 * I + 2 * G_ * N_ + H_, E_}}, {"conv.weight", {C, (int64_t)taps_}, false, 0, 0.5f}, {"conv.bias", {C}, false, 0, 0.3f},
+                {"dt_bias", {(int64_t)H_}, false, 0, 1.0f}, {"A_log", {(int64_t)H_}, false, 0, 1.0f}, {"D", {(int64_t)H_}, false, 1, 0.3f},
+                {"norm.weight", {I}, false, 1, 0.01f}, {"o_proj.weight", {E_, I}}};
+    }
+    bool can_overwrite() const override { return true; }
+    bool strided_state() const override { return true; }
+    int64_t state_bytes() const override {
+        return (conv_floats() + recurrence_state_floats(H_, N_, dv_, "state_space")) * (int64_t)sizeof(float);
+    }
+    void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
+        check_state_floats(H_, N_, dv_, "state_space");
+        in_ = Linear(tensor_of(tensors, "in_proj.weight"));
+        o_ = Linear(tensor_of(tensors, "o_proj.weight"));
+        conv_w_ = f32_rows({tensor_of(tensors, "conv.weight")}, rt.stream);
+        conv_b_ = f32_rows({tensor_of(tensors, "conv.bias")}, rt.stream);
+        dt_bias_ = f32_rows({tensor_of(tensors, "dt_bias")}, rt.stream);
+        a_log_ = f32_rows({tensor_of(tensors, "A_log")}, rt.stream);
+        skip_ = f32_rows({tensor_of(tensors, "D")}, rt.stream);
+        norm_ = f32_rows({tensor_of(tensors, "norm.weight")}, rt.stream);
+    }
+    DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *, const Batch &b, const LayerIO &io, Tensor &residual,
+                         Norm *emit_norm) override {
+        if (!io.state || io.state_bytes < state_bytes()) fail(FG_E_INTERNAL, "state_space: the schedule entry has no state rows");
+        const long long stride = (long long)(io.state_stride / (int64_t)sizeof(float));
+        const int I = (int)inner(), C = (int)conv_channels(), GN = G_ * N_;
+        Tensor proj = in_.forward(rt, xn, nullptr, Tensor(), FG_F32, false, nullptr, nullptr);
+        const int M = (int)proj.rows, ld = (int)proj.ld;
+        float *state = (float *)io.state;
+        Tensor xbc = rt.arena->matrix(M, C, FG_F32);
+        FG_LAUNCH("mix", fg_conv1d_silu, proj.ptr<float>() + I, ld, conv_w_.t.ptr<float>(), conv_b_.t.ptr<float>(), taps_, state, stride, b.row_seq, b.cu_rows,
+                  b.slots, xbc.ptr<float>(), (int)xbc.ld, M, C, rt.stream);
+        if (taps_ > 1)
+            FG_LAUNCH("mix", fg_conv1d_state, proj.ptr<float>() + I, ld, taps_, state, stride, b.cu_rows, b.slots, b.n_seq, C, rt.stream);
+        float *decay = (float *)rt.arena->alloc((size_t)2 * M * H_ * sizeof(float)), *step = decay + (size_t)M * H_;
+        FG_LAUNCH("mix", fg_decay_gates, proj.ptr<float>() + I + C, ld, nullptr, 0, a_log_.t.ptr<float>(), dt_bias_.t.ptr<float>(), 0, decay, step, M, H_,
+                  rt.stream);
+        Tensor y = rt.arena->matrix(M, I, FG_F32);
+        const int xl = (int)xbc.ld;
+        FG_LAUNCH("mix", fg_decay_recurrence, xbc.ptr<float>() + I + GN, xl, xbc.ptr<float>() + I, xl, xbc.ptr<float>(), xl, decay, step, skip_.t.ptr<float>(),
+                  y.ptr<float>(), (int)y.ld, b.cu_rows, b.slots, state + conv_floats(), stride, b.n_seq, H_, G_, N_, dv_, 0, rt.stream);
+        Tensor yn = rt.arena->matrix(M, I, rt.dtype);
+        FG_LAUNCH("mix", fg_gated_group_norm, y.ptr<float>(), (int)y.ld, proj.ptr<float>(), ld, norm_.t.ptr<float>(), I, yn.data, yn.dtype, (int)yn.ld, M, I,
+                  I / norm_groups_, eps_, 1, rt.stream);
+        DeferredNorm started;
+        o_.forward(rt, yn, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
+        return started;
+    }
+
+private:
+    int E_ = 0, H_ = 0, dv_ = 0, N_ = 0, G_ = 1, taps_ = 1, norm_groups_ = 1;
+    float eps_ = 0.f;
+    Linear in_, o_;
+    Weight conv_w_, conv_b_, dt_bias_, a_log_, skip_, norm_;
+};
+
+// "gated_delta": the gated delta rule.  With the normalised input h, n_kv_heads heads of q and k (size head_dim) and n_heads
+// heads of v (size v_head_dim), head h using q/k head h / (n_heads / n_kv_heads):
+//     q, k, v <- silu(causal convolution over time per channel of W_q h, W_k h, W_v h)      weights [channels, taps], no bias
+//     q <- q / sqrt(sum(q^2) + unit_eps) * q_scale and k <- k / sqrt(sum(k^2) + unit_eps), per head
+//     beta = sigmoid(W_b h), g = exp(-exp(A_log) softplus(W_a h + dt_bias)), one each per head
+//     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q                          (S: [head_dim, v_head_dim])
+//     y = o / sqrt(mean(o^2) + eps) * w (w [v_head_dim], shared by heads) * silu(W_g h); output W_o y
+// The six projections are ONE contraction with float32 output; everything up to y is float32 in every engine dtype.
+class GatedDeltaMixer : public Mixer {
+public:
+    GatedDeltaMixer(const Json &p, BuildContext &) {
+        const char *me = "gated_delta";
+        E_ = (int)param_int(p, "hidden_size", me);
+        H_ = (int)param_int(p, "n_heads", me);
+        G_ = (int)param_int(p, "n_kv_heads", H_, me);
+        d_ = (int)param_int(p, "head_dim", me);
+        dv_ = (int)param_int(p, "v_head_dim", d_, me);
+        taps_ = (int)param_int(p, "conv_taps", 1, me);
+        eps_ = (float)param_float(p, "eps", me);
+        unit_eps_ = (float)param_float(p, "unit_eps", 1e-6, me);
+        q_scale_ = (float)param_float(p, "q_scale", 1.0 / std::sqrt((double)d_), me);
+        if (E_ <= 0 || H_ <= 0 || G_ <= 0 || d_ <= 0 || dv_ <= 0 || taps_ <= 0) fail(FG_E_CONFIG, "gated_delta: sizes must be positive");
+        if (H_ % G_) fail(FG_E_CONFIG, format("gated_delta: %d heads are not a multiple of %d key heads", H_, G_));
+        if (d_ > 512) fail(FG_E_CONFIG, format("gated_delta: head_dim %d exceeds 512, the largest the kernel takes", d_));
+        if (!(eps_ > 0.f) || !(unit_eps_ >= 0.f)) fail(FG_E_CONFIG, "gated_delta: eps must be positive");
+    }
+    int64_t conv_channels() const { return (int64_t)2 * G_ * d_ + (int64_t)H_ * dv_; }
+    int64_t conv_floats() const { return (int64_t)(taps_ - 1) * conv_channels(); }
+    std::vector<TensorDecl> tensor_decls() const override {
+        const int64_t Q = (int64_t)G_ * d_, V = (int64_t)H_ * dv_;
+        return {{"q_proj.weight", {Q, E_}}, {"k_proj.weight", {Q, E_}}, {"v_proj.weight", {V, E_}}, {"b_proj.weight", {(int64_t)H_, E_}},
+                {"a_proj.weight", {(int64_t)H_, E_}}, {"g_proj.weight", {V, E_}}, {"o_proj.weight", {E_, V}},
+                {"q_conv.weight", {Q, (int64_t)taps_}, false, 0, 0.5f}, {"k_conv.weight", {Q, (int64_t)taps_}, false, 0, 0.5f},
+                {"v_conv.weight", {V, (int64_t)taps_}, false, 0, 0.5f}, {"A_log", {(int64_t)H_}, false, 0, 1.0f}, {"dt_bias", {(int64_t)H_}, false, 0, 1.0f},
+                {"norm.weight", {(int64_t)dv_}, false, 1, 0.01f}};
+    }
+    bool can_overwrite() const override { return true; }
+    bool strided_state() const override { return true; }
+    int64_t state_bytes() const override {
+        return (conv_floats() + recurrence_state_floats(H_, d_, dv_, "gated_delta")) * (int64_t)sizeof(float);
+    }
+    void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
+        check_state_floats(H_, d_, dv_, "gated_delta");
+        std::vector<Weight> rows;
+        bool same = true;
+        for (const char *n : {"q_proj.weight", "k_proj.weight", "v_proj.weight", "b_proj.weight", "a_proj.weight", "g_proj.weight"}) {
+            rows.push_back(tensor_of(tensors, n));
+            same = same && rows.back().t.dtype == rows.front().t.dtype;
+        }
+        proj_ = Linear(concat_rows(rows, same ? rows.front().t.dtype : FG_F32, rt.stream));
+        o_ = Linear(tensor_of(tensors, "o_proj.weight"));
+        // [channels, taps] row-major: the three lie one after another
+        conv_w_ = make_weight(conv_channels(), taps_, FG_F32, "convolution weights of the delta rule");
+        size_t at = 0;
+        for (const char *n : {"q_conv.weight", "k_conv.weight", "v_conv.weight"}) {
+            const Weight &w = tensor_of(tensors, n);
+            dev_convert(w.t.data, w.t.dtype, (char *)conv_w_.t.data + at * 4, FG_F32, w.t.numel(), rt.stream);
+            at += (size_t)w.t.numel();
+        }
+        a_log_ = f32_rows({tensor_of(tensors, "A_log")}, rt.stream);
+        dt_bias_ = f32_rows({tensor_of(tensors, "dt_bias")}, rt.stream);
+        norm_ = f32_rows({tensor_of(tensors, "norm.weight")}, rt.stream);
+    }
+    DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *, const Batch &b, const LayerIO &io, Tensor &residual,
+                         Norm *emit_norm) override {
+        if (!io.state || io.state_bytes < state_bytes()) fail(FG_E_INTERNAL, "gated_delta: the schedule entry has no state rows");
+        const long long stride = (long long)(io.state_stride / (int64_t)sizeof(float));
+        const int Q = G_ * d_, V = H_ * dv_, C = (int)conv_channels();
+        Tensor proj = proj_.forward(rt, xn, nullptr, Tensor(), FG_F32, false, nullptr, nullptr);
+        const int M = (int)proj.rows, ld = (int)proj.ld;
+        float *state = (float *)io.state;
+        Tensor qkv = rt.arena->matrix(M, C, FG_F32);
+        const int xl = (int)qkv.ld;
+        FG_LAUNCH("mix", fg_conv1d_silu, proj.ptr<float>(), ld, conv_w_.t.ptr<float>(), nullptr, taps_, state, stride, b.row_seq, b.cu_rows, b.slots,
+                  qkv.ptr<float>(), xl, M, C, rt.stream);
+        if (taps_ > 1) FG_LAUNCH("mix", fg_conv1d_state, proj.ptr<float>(), ld, taps_, state, stride, b.cu_rows, b.slots, b.n_seq, C, rt.stream);
+        FG_LAUNCH("mix", fg_unit_heads, qkv.ptr<float>(), xl, G_, d_, unit_eps_, q_scale_, M, rt.stream);
+        FG_LAUNCH("mix", fg_unit_heads, qkv.ptr<float>() + Q, xl, G_, d_, unit_eps_, 1.0f, M, rt.stream);
+        float *decay = (float *)rt.arena->alloc((size_t)2 * M * H_ * sizeof(float)), *step = decay + (size_t)M * H_;
+        FG_LAUNCH("mix", fg_decay_gates, proj.ptr<float>() + C + H_, ld, proj.ptr<float>() + C, ld, a_log_.t.ptr<float>(), dt_bias_.t.ptr<float>(), 1, decay,
+                  step, M, H_, rt.stream);
+        Tensor o = rt.arena->matrix(M, V, FG_F32);
+        FG_LAUNCH("mix", fg_decay_recurrence, qkv.ptr<float>(), xl, qkv.ptr<float>() + Q, xl, qkv.ptr<float>() + 2 * Q, xl, decay, step, nullptr, o.ptr<float>(),
+                  (int)o.ld, b.cu_rows, b.slots, state + conv_floats(), stride, b.n_seq, H_, G_, d_, dv_, 1, rt.stream);
+        Tensor y = rt.arena->matrix(M, V, rt.dtype);
+        FG_LAUNCH("mix", fg_gated_group_norm, o.ptr<float>(), (int)o.ld, proj.ptr<float>() + C + 2 * H_, ld, norm_.t.ptr<float>(), dv_, y.data, y.dtype,
+                  (int)y.ld, M, V, dv_, eps_, 0, rt.stream);
+        DeferredNorm started;
+        o_.forward(rt, y, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
+        return started;
+    }
+
+private:
+    int E_ = 0, H_ = 0, G_ = 0, d_ = 0, dv_ = 0, taps_ = 1;
+    float eps_ = 0.f, unit_eps_ = 1e-6f, q_scale_ = 1.f;
+    Linear proj_, o_;
+    Weight conv_w_, a_log_, dt_bias_, norm_;
+};
+
 void add_recurrent_kinds(std::map<std::string, PartFactory> &mixers) {
     mixers["gated_linear_attention"] = [](Runtime &, const Json &p, BuildContext &c) { return std::make_unique<GatedLinearAttention>(p, c); };
     mixers["retention"] = [](Runtime &, const Json &p, BuildContext &c) { return std::make_unique<RetentionMixer>(p, c); };
+    mixers["state_space"] = [](Runtime &, const Json &p, BuildContext &c) { return std::make_unique<StateSpaceMixer>(p, c); };
+    mixers["gated_delta"] = [](Runtime &, const Json &p, BuildContext &c) { return std::make_unique<GatedDeltaMixer>(p, c); };
 }
 
 }  // namespace fg

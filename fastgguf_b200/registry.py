@@ -19,9 +19,10 @@ from .config.llama import LlamaConfig
 from .config.zirivik import ZirivikConfig
 from .config.salulorn import SalulornConfig
 from .config.pirozen import PirozenConfig
+from .config.saluzen import SaluzenConfig
 from .engine.spec import ModelSpec
 
-_CLASSES = {"LlamaForCausalLM": LlamaConfig, "Zirivik": ZirivikConfig, "Salulorn": SalulornConfig, "Pirozen": PirozenConfig}
+_CLASSES = {"LlamaForCausalLM": LlamaConfig, "Zirivik": ZirivikConfig, "Salulorn": SalulornConfig, "Pirozen": PirozenConfig, "Saluzen": SaluzenConfig}
 _keep_alive = []
 
 
