@@ -1,0 +1,548 @@
+"""The Saluzen decoder in the engine against the plain implementation (``plain_saluzen``): each mechanism alone, whole
+prompts, portions, decoding, batches, reused slots and pages, and generation through the entry point.
+
+Structure is tested in float32, where any key wrongly seen or missed, any state lost or kept too long is orders of
+magnitude above the tolerance; the bfloat16 runs use sharpened attention (see ``saluzen_cases.random_weights``) so that
+the same faults stay visible above rounding."""
+import numpy as np
+import pytest
+import torch
+
+import plain_saluzen as ps
+from helpers import rel_err
+from saluzen_cases import CASES, attn, config, delta, dense, latent, make_model, parallel, parallel_2, random_weights, ssm, write_model
+
+pytestmark = pytest.mark.gpu
+
+#: max |dlogit| / max |logit| against the float64 plain implementation.  float32: a key wrongly seen or a lost state is at 1e-3
+#: and above.  bfloat16 with sharpened attention: rounding reaches a few 1e-2, a structural fault 0.3 and more
+TOL = {"float32": 2e-5, "bfloat16": 1e-1}
+
+
+def tokens_for(cfg, n, seed):
+    rng = np.random.default_rng(seed)
+    return [int(t) for t in rng.integers(0, cfg["vocab"], size=n)]
+
+
+def engine_for(model_dir, dtype, **kw):
+    from fastgguf_b200.engine.api import Engine
+    args = dict(dtype=dtype, max_tokens=4096, max_batch=8)
+    args.update(kw)
+    return Engine.from_dir(model_dir, **args)
+
+
+def entry(slot, toks, want=None):
+    from fastgguf_b200.engine.batch import StepEntry
+    return StepEntry(slot, toks, list(range(len(toks))) if want is None else want)
+
+
+def plain_logits(cfg, W, toks):
+    return ps.forward(cfg, W, toks).numpy()
+
+
+def f32(x):
+    return np.ascontiguousarray(x.numpy() if hasattr(x, "numpy") else x, dtype=np.float32)
+
+
+class Rows:
+    """Collects the errors of a whole model's logits, row by row, and judges them.
+
+    Every sublayer's output is normalised whatever its size, so where a mixer returns little (a sequence's first tokens, a
+    chunk's first rows) every rounding in it is amplified, in float32 as in bfloat16.  At most one row in fifty (or one row)
+    may exceed the tolerance: a key wrongly seen or a lost state moves many rows by far more.  In float32 none may exceed
+    three times the tolerance.  In bfloat16 a rare row has no such bound: sharpened scores let two keys compete so closely
+    that rounding decides between them (the float64 implementation with nothing but its norms' outputs rounded to bfloat16
+    moves one row in 150 of the first case by 0.26 of its largest logit, the others by 0.01)."""
+
+    def __init__(self, dtype):
+        self.dtype, self.n, self.over = dtype, 0, []
+
+    def add(self, got, want, what):
+        e = rel_err(got, want)
+        self.n += 1
+        assert self.dtype == "bfloat16" or e < 3 * TOL[self.dtype], (what, e)
+        if e >= TOL[self.dtype]:
+            self.over.append((what, e))
+
+    def done(self):
+        assert len(self.over) <= max(1, self.n // 50), self.over
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    """(case, 1.0): the case as it is; (case, 1.5): attention sharpened, for bfloat16 (queries and keys alike, so scores grow by 2.25; the heads have no norm that would take it back)."""
+    out = {}
+    for i, (name, cfg) in enumerate(CASES.items()):
+        for sharp in (1.0, 1.5):
+            d, W = make_model(tmp_path_factory.mktemp(f"z_{name}_{int(sharp)}"), cfg, 100 + i, sharp)
+            out[(name, sharp)] = (d, cfg, W)
+    return out
+
+
+# ------------------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("scaling", [None, (8.0, 1.0, 4.0, 256), (3.0, 2.0, 5.0, 40)])
+def test_rotary_tables_with_and_without_scaling(scaling):
+    """The tables the rotation kernels read: pair i of a position holds cos / sin of position * frequency, frequencies
+    kept, divided or blended by their wavelength."""
+    from fastgguf_b200.parts import position_tables
+    rot = {"base": 5000.0, "dims": 24}
+    params = {"head_dim": 32, "theta": 5000.0, "rotary_dim": 24, "layout": "halves", "scaling": None}
+    if scaling:
+        rot["scaling"] = dict(zip(("factor", "low", "high", "original"), scaling))
+        params["scaling"] = {"rope_type": "llama3", "factor": scaling[0], "low_freq_factor": scaling[1], "high_freq_factor": scaling[2],
+                             "original_max_position_embeddings": scaling[3]}
+    cos, sin, _ = position_tables("rope", params, 300)
+    f = ps.rotary_frequencies(rot)
+    ang = torch.arange(300, dtype=torch.float64)[:, None] * f[None, :]
+    assert np.abs(cos[:, :12] - torch.cos(ang).numpy()).max() < 2e-6
+    assert np.abs(sin[:, :12] - torch.sin(ang).numpy()).max() < 2e-6
+    assert np.all(cos[:, 12:] == 1.0) and np.all(sin[:, 12:] == 0.0)       # dimensions that are not rotated
+    if scaling:
+        plain = ps.rotary_frequencies({"base": 5000.0, "dims": 24})
+        ratio = (plain / f).numpy()
+        assert ratio.min() == 1.0 and abs(ratio.max() - scaling[0]) < 1e-9 and np.any((ratio > 1.001) & (ratio < scaling[0] - 0.001))
+
+
+def one_layer(layer, mlp=None, width=80, vocab=50):
+    return config(width, vocab, [(layer, mlp)])
+
+
+def only(side):
+    """An edit of the weights that silences the other side of a pair: its share of a weighted pair is what the file's scale
+    says (the cases below give 0), its share of a normalised pair vanishes with a zero weight behind its norm."""
+    def change(W):
+        other = "right" if side == "left" else "left"
+        if f"l0.mix.{other}.out" in W:
+            W[f"l0.mix.{other}.out"] = torch.zeros_like(W[f"l0.mix.{other}.out"])
+    return change
+
+
+A_SMALL = attn(2, 1, 16, 16, 0.25)
+S_SMALL = ssm(2, 8, 8, 1, 2, 1)
+D_SMALL = delta(2, 1, 8, 8, 2)
+MIXERS = {
+    # (layer, which side is heard; None: both)
+    "attention with a unit sink, a gate per number, some dimensions rotated": (parallel(attn(4, 2, 24, 40, 0.3, rot=(100.0, 12)), S_SMALL), "left"),
+    "attention with a unit sink, scaled frequencies, one key head": (parallel(attn(3, 1, 16, 16, 0.4, rot=(50.0, 16), scaling=(6.0, 1.0, 3.0, 16)), S_SMALL), "left"),
+    "attention in chunks of 5, learned sinks, a gate per head": (parallel_2(attn(6, 3, 16, 8, 0.4, rot=(10000.0, 16), size=5), D_SMALL, 1.5, 0.0), "left"),
+    "attention in chunks of 1, no rotation": (parallel_2(attn(2, 2, 16, 16, 0.5, size=1), D_SMALL, 0.5, 0.0), "left"),
+    "state space, small": (parallel(A_SMALL, ssm(3, 24, 16, 1, 4, 1)), "right"),
+    "state space, groups as heads, norm groups inside a head, two taps": (parallel(A_SMALL, ssm(4, 16, 24, 4, 2, 8)), "right"),
+    "state space, one tap, one head": (parallel(A_SMALL, ssm(1, 40, 20, 1, 1, 5)), "right"),
+    "delta rule, small": (parallel_2(A_SMALL, delta(4, 2, 16, 24, 2), 0.0, 1.25), "right"),
+    "delta rule, one key head, one tap, value size that does not fill a warp": (parallel_2(A_SMALL, delta(6, 1, 8, 12, 1), 0.0, 0.5), "right"),
+    "delta rule, keys of 48, four taps": (parallel_2(A_SMALL, delta(2, 2, 48, 16, 4), 0.0, 1.0), "right"),
+    "both sides of a normalised pair": (parallel(attn(4, 2, 24, 40, 0.3, rot=(100.0, 12)), ssm(3, 24, 16, 1, 4, 1)), None),
+    "both sides of a weighted pair": (parallel_2(attn(6, 3, 16, 8, 0.4, size=5), delta(4, 2, 16, 24, 2), 0.8, 0.5), None),
+    "latent attention, small": (latent(3, 16, 8, 24, 40, 48, 0.2, 10000.0), None),
+    "latent attention, one head": (latent(1, 8, 16, 8, 12, 20, 0.3, 500.0), None),
+    "long attention, unit sink, head 64": (parallel(attn(4, 2, 64, 64, 0.125, rot=(250000.0, 64), scaling=(4.0, 1.0, 4.0, 128)), S_SMALL), "left"),
+    "long attention, chunks past a page, head 128, five query heads a key head": (parallel_2(attn(5, 1, 128, 128, 0.09, rot=(1000.0, 32), size=70), D_SMALL, 1.0, 0.0), "left"),
+    "long attention, chunks of a page, keys 128 and values 64": (parallel_2(attn(2, 1, 128, 64, 0.09, size=64), D_SMALL, 1.0, 0.0), "left"),
+    "long state space, state 128, head 64": (parallel(A_SMALL, ssm(2, 64, 128, 1, 4, 2)), "right"),
+    "long state space, state 16, sixteen heads": (parallel(A_SMALL, ssm(16, 32, 16, 2, 3, 1)), "right"),
+    "long delta rule, head 128": (parallel_2(A_SMALL, delta(2, 1, 128, 128, 3), 0.0, 1.0), "right"),
+    "long delta rule, keys 64 and values 256": (parallel_2(A_SMALL, delta(4, 2, 64, 256, 2), 0.0, 0.7), "right"),
+    "long latent attention, latent of 128, heads of 128 for whole prompts": (latent(3, 96, 32, 128, 128, 80, 0.09, 50000.0), None),
+}
+
+
+def layer_alone(x, W, layer, eps=1e-5):
+    """what one sandwich layer without a feed-forward makes of the rows x"""
+    h = ps.rms_norm(x, W["l0.norm1"], eps)
+    if layer["type"] == "latent_attention":
+        y = ps.latent_attention(h, W, "l0.mix.", layer["mixer"], eps, ps.latent_kv(h, W, "l0.mix.", layer["mixer"], eps))
+    else:
+        y = ps.pair_mixer(h, W, "l0.mix.", layer, eps)
+    return x + ps.rms_norm(y, W["l0.norm1b"], eps)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(MIXERS))
+def test_mixer_alone(tmp_path, name, dtype):
+    """One layer of a mixer alone (norm, mixer, norm, residual add) on rows given by the test: a portion of 37 rows, then one
+    of 2, then single rows, so the second and later calls start from what the first left behind (the long cases: 160, 30
+    and 2 rows, then 38 single ones).  Where one side of a pair is tested the other is silenced, and the test says that
+    the side that is heard matters."""
+    layer, side = MIXERS[name]
+    cfg = one_layer(layer)
+    d, W = make_model(tmp_path, cfg, 7, sharp=2.0, change=only(side) if side else None)
+    eng = engine_for(d, dtype)
+    g = torch.Generator().manual_seed(8)
+    cuts = [160, 30, 2] + [1] * 38 if name.startswith("long") else [37, 2, 1, 1, 1, 1, 1, 1]
+    T = sum(cuts)
+    x = torch.randn(T, cfg["width"], generator=g, dtype=torch.float64)
+    want = layer_alone(x, W, layer).numpy()
+    assert np.abs(want - x.numpy()).max() > 0.1
+    slot = eng.acquire()
+    got, at = [], 0
+    for n in cuts:
+        got.append(eng.block_forward(0, [(slot, n)], f32(x[at:at + n])))
+        at += n
+    got = np.concatenate(got)
+    tol = 2e-5 if dtype == "float32" else 5e-2
+    for r in range(T):
+        assert rel_err(got[r], want[r]) < tol, (name, r)
+
+
+@pytest.mark.parametrize("name", ["long attention, unit sink, head 64", "long attention, chunks past a page, head 128, five query heads a key head",
+                                  "long latent attention, latent of 128, heads of 128 for whole prompts", "long delta rule, head 128"])
+def test_a_wide_batch_of_prompts(tmp_path, name):
+    """Four prompts of 5 to 800 tokens in one step, sequences x longest prompt beyond 3,072: the tensor-core attention then runs
+    its form with two sets of softmax warps, in which a row's sink must still count once.  Then one more token each."""
+    layer, side = MIXERS[name]
+    cfg = one_layer(layer)
+    d, W = make_model(tmp_path, cfg, 12, sharp=2.0, sink=2.0, change=only(side) if side else None)
+    eng = engine_for(d, "bfloat16", max_tokens=4096, max_batch=4)
+    g = torch.Generator().manual_seed(9)
+    lens = [800, 300, 50, 5]
+    xs = [torch.randn(n + 1, cfg["width"], generator=g, dtype=torch.float64) for n in lens]
+    want = [layer_alone(x, W, layer).numpy() for x in xs]
+    slots = [eng.acquire() for _ in lens]
+    got = eng.block_forward(0, list(zip(slots, lens)), f32(torch.cat([x[:n] for x, n in zip(xs, lens)])))
+    at = 0
+    for b, n in enumerate(lens):
+        for r in (0, 1, n // 2, n - 2, n - 1):
+            assert rel_err(got[at + r], want[b][r]) < 5e-2, (name, b, r)
+        at += n
+    got = eng.block_forward(0, [(s, 1) for s in slots], f32(torch.stack([x[n] for x, n in zip(xs, lens)])))
+    for b, n in enumerate(lens):
+        assert rel_err(got[b], want[b][n]) < 5e-2, (name, b, "decoded")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_with_both_sublayers(tmp_path, dtype):
+    """x <- x + norm(mixer(norm(x))), then x <- x + norm(ff(norm(x))): four norms a layer, each with a weight of its own."""
+    layer = parallel(attn(2, 1, 16, 16, 0.25, rot=(100.0, 8)), ssm(2, 16, 8, 1, 3, 2))
+    cfg = one_layer(layer, dense(56))
+    d, W = make_model(tmp_path, cfg, 9)
+    eng = engine_for(d, dtype)
+    x = torch.randn(20, 80, generator=torch.Generator().manual_seed(1), dtype=torch.float64)
+    mid = layer_alone(x, W, layer)
+    want = mid + ps.rms_norm(ps.dense_ff(ps.rms_norm(mid, W["l0.norm2"], 1e-5), W, "l0.mlp."), W["l0.norm2b"], 1e-5)
+    got = eng.block_forward(0, [(eng.acquire(), 20)], f32(x))
+    assert rel_err(got, want.numpy()) < (1e-5 if dtype == "float32" else 3e-2)
+    assert rel_err(got, mid.numpy()) > 1e-2            # the feed-forward is there
+
+
+def test_sinks_take_weight_from_the_keys(tmp_path):
+    """The unit sink and large learned sinks shrink what attention returns; the engine follows the plain implementation, and
+    both differ by far from a softmax without a sink."""
+    x = torch.randn(30, 80, generator=torch.Generator().manual_seed(2), dtype=torch.float64)
+    for layer in (parallel(attn(3, 1, 16, 24, 0.3), S_SMALL), parallel_2(attn(3, 1, 16, 24, 0.3, size=12), D_SMALL, 1.0, 0.0)):
+        cfg = one_layer(layer)
+        d, W = make_model(tmp_path / layer["type"], cfg, 10, sink=4.0, change=only("left"))
+        eng = engine_for(d, "float32")
+        h = ps.rms_norm(x, W["l0.norm1"], 1e-5)
+        kind = ("one", "full") if layer["type"] == "parallel" else ("learned", "head")
+        m = layer["mixer"]["left"]
+        with_sink = ps.gated_attention(h, W, "l0.mix.left.", m, *kind)
+        far = dict(W)
+        far["l0.mix.left.sink"] = torch.full((3,), -1e4, dtype=torch.float64)
+        without = ps.gated_attention(h, far, "l0.mix.left.", m, "learned", kind[1])
+        assert rel_err(without.numpy(), with_sink.numpy()) > 1e-2
+        got = eng.block_forward(0, [(eng.acquire(), 30)], f32(x))
+        assert rel_err(got, layer_alone(x, W, layer).numpy()) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("size", [7, 64, 65, 96])
+def test_one_key_at_a_chunks_edge(tmp_path, size, dtype):
+    """Weights and inputs made so that ONE key far outweighs all others for every later query: the key projection is the
+    query projection with its input columns shifted, the special row is the later rows' common direction shifted back.
+    The last row of the special key's chunk returns its value, the first row of the next chunk does not - in a prompt
+    and decoded one by one."""
+    layer = parallel_2(attn(2, 1, 16, 16, 1.0, size=size), D_SMALL, 1.0, 0.0)
+    cfg = one_layer(layer)
+    E = 80
+    special = size + 3                              # the fourth key of the second chunk
+    last_in, first_out = 2 * size - 1, 2 * size
+    T = first_out + 20
+    W = random_weights(cfg, 11)
+    W["l0.mix.left.q"] = W["l0.mix.left.q"][:16].repeat(2, 1)                 # both query heads ask the one key head the same
+    W["l0.mix.left.k"] = torch.roll(W["l0.mix.left.q"][:16], 1, dims=1)      # k(h) = q(h shifted back by one column)
+    for k in ("l0.mix.left.q.b", "l0.mix.left.k.b"):
+        W[k] = torch.zeros_like(W[k])
+    W["l0.norm1"] = torch.ones_like(W["l0.norm1"])
+    W["l0.mix.left.sink"] = torch.full_like(W["l0.mix.left.sink"], -20.0)
+    W["l0.mix.left.g"] = torch.zeros_like(W["l0.mix.left.g"])
+    d = write_model(tmp_path, cfg, W)
+    W = {k: v.double() for k, v in W.items()}
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(T, E, generator=g, dtype=torch.float64)
+    w = torch.randn(E, generator=g, dtype=torch.float64)
+    x[special] = torch.roll(w, 1)                                   # its key is the query of direction w
+    x[special + 1:] = w[None, :] + 0.05 * x[special + 1:]
+    h = ps.rms_norm(x, W["l0.norm1"], 1e-5)
+    mixed = ps.gated_attention(h, W, "l0.mix.left.", layer["mixer"]["left"], "learned", "head").numpy()
+    assert np.abs(mixed[last_in] - mixed[first_out]).max() > 0.3 * np.abs(mixed[last_in]).max()      # the edge shows
+    want = layer_alone(x, W, layer).numpy()
+    tol = 2e-5 if dtype == "float32" else 5e-2
+    for cuts in ([T], [special + 1] + [1] * (T - special - 1)):
+        eng = engine_for(d, dtype)
+        slot, at, got = eng.acquire(), 0, []
+        for n in cuts:
+            got.append(eng.block_forward(0, [(slot, n)], f32(x[at:at + n])))
+            at += n
+        got = np.concatenate(got)
+        for r in (size - 1, size, special, special + 1, last_in - 1, last_in, first_out, first_out + 1, T - 1):
+            assert rel_err(got[r], want[r]) < tol, (size, cuts[0], r)
+
+
+def test_a_state_that_forgets_slowly_carries_one_token(tmp_path):
+    """One early row differs between two inputs of 300 rows: through the slowly decaying states the last rows differ by far
+    more than rounding, in the engine exactly as in the plain implementation, in a prompt and across portions."""
+    for layer, name in ((parallel(A_SMALL, ssm(2, 16, 16, 1, 3, 1)), "ssm"), (parallel_2(A_SMALL, delta(2, 1, 16, 16, 3), 0.0, 1.0), "delta")):
+        cfg = one_layer(layer)
+        d, W = make_model(tmp_path / name, cfg, 60, slow=4.0, change=only("right"))
+        g = torch.Generator().manual_seed(4)
+        xa = torch.randn(300, 80, generator=g, dtype=torch.float64)
+        xb = xa.clone()
+        xb[3] = torch.randn(80, generator=g, dtype=torch.float64)
+        eng = engine_for(d, "float32")
+        last = []
+        for x in (xa, xb):
+            want = layer_alone(x, W, layer).numpy()
+            s = eng.acquire()
+            got = np.concatenate([eng.block_forward(0, [(s, n)], f32(x[a:a + n])) for a, n in ((0, 2), (2, 198), (200, 99), (299, 1))])
+            eng.release(s)
+            assert rel_err(got[-1], want[-1]) < 2e-5
+            last.append(got[-1] - x[-1].numpy())
+        assert np.abs(last[0] - last[1]).max() > 1e-3 * np.abs(last[0]).max(), name
+
+
+# ------------------------------------------------------------------------------ whole models
+@pytest.mark.parametrize("dtype,sharp", [("float32", 1.0), ("bfloat16", 1.5)])
+@pytest.mark.parametrize("which", list(CASES))
+def test_whole_prompt(models, which, dtype, sharp):
+    """Logits at every position of a prompt that passes every chunk and page edge of the case."""
+    d, cfg, W = models[(which, sharp)]
+    toks = tokens_for(cfg, 150, 11)
+    want = plain_logits(cfg, W, toks)
+    eng = engine_for(d, dtype)
+    s = eng.acquire()
+    got = eng.step_host([entry(s, toks)])
+    judge = Rows(dtype)
+    for p in range(len(toks)):
+        judge.add(got[p], want[p], (which, p))
+    judge.done()
+    eng.release(s)
+    eng.cache.check()
+
+
+def test_the_first_tokens(models):
+    """Sequences of one, two, three and five tokens, as a prompt and one by one: convolutions that reach in front of the
+    sequence's start see zeros, states start at zero, the first chunk starts at the first position."""
+    for which in CASES:
+        d, cfg, W = models[(which, 1.0)]
+        eng = engine_for(d, "float32")
+        for n in (1, 2, 3, 5):
+            toks = tokens_for(cfg, n, 30 + n)
+            want = plain_logits(cfg, W, toks)
+            s = eng.acquire()
+            assert rel_err(eng.step_host([entry(s, toks)]), want) < TOL["float32"], (which, n)
+            eng.release(s)
+            s = eng.acquire()
+            got = np.concatenate([eng.step_host([entry(s, [t])]) for t in toks])
+            assert rel_err(got, want) < TOL["float32"], (which, n)
+            eng.release(s)
+
+
+@pytest.mark.parametrize("dtype,sharp", [("float32", 1.0), ("bfloat16", 1.5)])
+@pytest.mark.parametrize("which,cuts", [("a", [2, 2, 3, 17, 33, 64, 65, 2, 31]), ("b", [63, 2, 64, 1, 1, 70, 2, 16]),
+                                        ("c", [100, 28, 1, 2, 64, 24]), ("d", [3, 2, 40, 2])])
+def test_portions_and_decoding(models, which, cuts, dtype, sharp):
+    """A prompt cut into portions of many sizes, down to two tokens and one, then 40 tokens one by one: the same logits
+    as the whole sequence at every position."""
+    d, cfg, W = models[(which, sharp)]
+    n = sum(cuts) + 40
+    toks = tokens_for(cfg, n, 13)
+    want = plain_logits(cfg, W, toks)
+    eng = engine_for(d, dtype)
+    s = eng.acquire()
+    at = 0
+    judge = Rows(dtype)
+    for c in cuts + [1] * 40:
+        got = eng.step_host([entry(s, toks[at:at + c])])
+        for i in range(c):
+            judge.add(got[i], want[at + i], (which, at + i, c))
+        at += c
+    judge.done()
+    eng.release(s)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype,sharp", [("float32", 1.0), ("bfloat16", 1.5)])
+@pytest.mark.parametrize("which", list(CASES))
+def test_batch_of_unequal_requests(models, which, dtype, sharp):
+    """Five requests of 1 to 140 tokens in one step, then decoded together while the shorter ones leave: every
+    request's logits equal those it has alone."""
+    d, cfg, W = models[(which, sharp)]
+    lens, total = [1, 140, 64, 7, 65], [9, 150, 70, 30, 66]
+    toks = [tokens_for(cfg, t, 20 + i) for i, t in enumerate(total)]
+    want = [plain_logits(cfg, W, t) for t in toks]
+    eng = engine_for(d, dtype)
+    slots = [eng.acquire() for _ in toks]
+    got = eng.step_host([entry(s, t[:n]) for s, t, n in zip(slots, toks, lens)])
+    row = 0
+    judge = Rows(dtype)
+    for b, n in enumerate(lens):
+        for p in range(n):
+            judge.add(got[row], want[b][p], (which, b, p))
+            row += 1
+    at = list(lens)
+    alive = list(range(len(toks)))
+    while alive:
+        got = eng.step_host([entry(slots[b], [toks[b][at[b]]]) for b in alive])
+        for i, b in enumerate(alive):
+            judge.add(got[i], want[b][at[b]], (which, b, at[b]))
+            at[b] += 1
+        for b in [b for b in alive if at[b] == total[b]]:
+            eng.release(slots[b])
+            alive.remove(b)
+    judge.done()
+    eng.cache.check()
+    assert eng.cache.live_slots() == []
+
+
+def test_slots_and_pages_used_again(models):
+    """Sequences come and go in a cache of two slots and few pages: a new sequence starts from nothing (state rows - the
+    recurrences' and the convolutions' - are cleared, pages of the one before are not read), also after a sequence that
+    was released halfway."""
+    d, cfg, W = models[("b", 1.0)]
+    eng = engine_for(d, "float32", max_tokens=512, max_batch=2)
+    seqs = [tokens_for(cfg, n, 40 + i) for i, n in enumerate([200, 130, 90, 260, 70, 140])]
+    for k, toks in enumerate(seqs):
+        s = eng.acquire()
+        other = eng.acquire()
+        eng.step_host([entry(other, seqs[(k + 1) % len(seqs)][:50], [])])       # a neighbour that is dropped halfway
+        want = plain_logits(cfg, W, toks)
+        head = len(toks) - 20
+        got = eng.step_host([entry(s, toks[:head], [head - 1])])
+        assert rel_err(got[0], want[head - 1]) < TOL["float32"], k
+        eng.release(other)
+        for p in range(head, len(toks)):
+            got = eng.step_host([entry(s, [toks[p]])])
+            assert rel_err(got[0], want[p]) < TOL["float32"], (k, p)
+        eng.release(s)
+        eng.cache.check()
+
+
+def test_long_decoding_past_chunks_and_pages(models):
+    """300 tokens one by one after a short prompt: chunks end and begin among decoded tokens, pages fill up, and the
+    recurrent states carry the first tokens all along."""
+    d, cfg, W = models[("b", 1.0)]
+    toks = tokens_for(cfg, 330, 50)
+    want = plain_logits(cfg, W, toks)
+    eng = engine_for(d, "float32")
+    s = eng.acquire()
+    eng.step_host([entry(s, toks[:30], [])])
+    for p in range(30, 330):
+        got = eng.step_host([entry(s, [toks[p]])])
+        assert rel_err(got[0], want[p]) < TOL["float32"], p
+    eng.release(s)
+    eng.cache.check()
+
+
+def test_a_far_token_is_remembered(tmp_path):
+    """One early token differs between two prompts of 400 tokens: through latent attention over all keys, and through a
+    state that forgets slowly, the last logits differ by far more than rounding, in the engine exactly as in the plain
+    implementation; through attention in short chunks alone they would not."""
+    short = attn(2, 1, 16, 16, 0.25, rot=(1000.0, 16), size=8)
+    for name, layers, slow in (("latent", [(latent(2, 16, 8, 16, 24, 24, 0.4, 10000.0), dense(48)), (parallel_2(short, D_SMALL, 1.0, 0.0), None)], 0.0),
+                               ("state", [(parallel_2(short, delta(2, 1, 16, 16, 2), 0.5, 1.0), dense(48))], 5.0)):
+        cfg = config(64, 90, layers)
+        d, W = make_model(tmp_path / name, cfg, 60, sharp=2.0, slow=slow)
+        a = tokens_for(cfg, 400, 61)
+        b = list(a)
+        b[3] = (a[3] + 1) % cfg["vocab"]
+        eng = engine_for(d, "float32")
+        last = []
+        for toks in (a, b):
+            s = eng.acquire()
+            got = eng.step_host([entry(s, toks[:380], [])])
+            for p in range(380, 400):
+                got = eng.step_host([entry(s, [toks[p]])])
+            last.append(got[0])
+            eng.release(s)
+            assert rel_err(got[0], plain_logits(cfg, W, toks)[-1]) < TOL["float32"]
+        # (rounding is at 1e-6 of the largest logit)
+        assert np.abs(last[0] - last[1]).max() > 1e-4 * np.abs(last[0]).max(), (name, np.abs(last[0] - last[1]).max() / np.abs(last[0]).max())
+
+
+# ------------------------------------------------------------------------------ generation through the entry point
+@pytest.mark.parametrize("use_graphs", [False, True])
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_greedy_generation(models, which, use_graphs):
+    """Greedy decoding through Engine.generate - the scheduler's batches, the recorded decode step, slots that come
+    back - follows the plain implementation: each token is the plain logits' best given the tokens before it (where the
+    best two are closer than rounding, either counts)."""
+    d, cfg, W = models[(which, 1.0)]
+    prompts = [tokens_for(cfg, n, 70 + i) for i, n in enumerate([5, 70, 1, 33, 12])]
+    eng = engine_for(d, "float32", max_tokens=2048, max_batch=4, use_graphs=use_graphs)
+    out = eng.generate(prompts, temp=0, max_tokens=24, ignore_eos=True, batch_size=3)
+    for p, c in zip(prompts, out):
+        assert len(c.tokens) == 24
+        logits = plain_logits(cfg, W, p + c.tokens)
+        for i, t in enumerate(c.tokens):
+            row = logits[len(p) + i - 1]
+            assert row[t] >= row.max() - 1e-4 * np.abs(row).max(), (which, i)
+    eng.cache.check()
+    assert eng.cache.live_slots() == []
+
+
+def test_generation_in_bfloat16_runs_the_recorded_step(models):
+    d, cfg, W = models[("c", 1.0)]
+    prompts = [tokens_for(cfg, n, 80 + i) for i, n in enumerate([9, 40])]
+    eng = engine_for(d, "bfloat16", max_tokens=1024, max_batch=2)
+    out = eng.generate(prompts, temp=0, max_tokens=70, ignore_eos=True)
+    for p, c in zip(prompts, out):
+        logits = plain_logits(cfg, W, p + c.tokens)
+        close = sum(logits[len(p) + i - 1][t] >= logits[len(p) + i - 1].max() - 0.05 * np.abs(logits[len(p) + i - 1]).max()
+                    for i, t in enumerate(c.tokens))
+        assert close >= 0.9 * len(c.tokens)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("which", ["a", "c"])
+def test_trace_replay_three_cuts(tmp_path, models, which):
+    """``bin/trace_run`` on a Saluzen folder in true 32-bit: the same requests whole, with their last 32 tokens one by one, and
+    in batches of four unequal requests one batch after another (slots and pages are used again); a cache that holds just what
+    the live requests need."""
+    from trace_tools import batched_trace, collect, run_trace, tail_trace, whole_trace
+    d, cfg, W = models[(which, 1.0)]
+    lengths = [5, 9, 1, 17, 3, 40, 11, 70, 33, 130]
+    requests = {f"r{i}": tokens_for(cfg, n, 100 + i) for i, n in enumerate(lengths)}
+    want = {rid: plain_logits(cfg, W, toks) for rid, toks in requests.items()}
+    need = max(sum((len(requests[r]) + 63) // 64 * 64 for r in list(requests)[b:b + 4]) for b in range(0, 10, 4))
+    cuts = {}
+    for name, (steps, index), room in (("whole", whole_trace(requests), 192), ("tail", tail_trace(requests, 32), 192),
+                                       ("batched", batched_trace(requests, 4), need)):
+        run_trace(d, "float32", steps, str(tmp_path / name), max_tokens=room)
+        rows = collect(str(tmp_path / name), steps, index, cfg["vocab"])
+        assert len(rows) == sum(lengths), name
+        for (rid, pos), row in rows.items():
+            assert rel_err(row, want[rid][pos]) < TOL["float32"], (name, rid, pos)
+        cuts[name] = rows
+    for key, row in cuts["whole"].items():
+        scale = np.abs(row).max()
+        assert np.abs(row - cuts["tail"][key]).max() < 2e-5 * scale and np.abs(row - cuts["batched"][key]).max() < 2e-5 * scale, key
+
+
+def test_command_line_generates(models):
+    """``python -m fastgguf_b200 generate`` on a Saluzen folder: the model class comes from config.json, the tokens are
+    those of Engine.generate."""
+    import json
+    import os
+    import subprocess
+    import sys
+    d, cfg, W = models[("a", 1.0)]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "fastgguf_b200", "generate", d, "256", "--prompt", "5,17,3,200", "--prompt", "9",
+                        "--temp", "0", "--max-tokens", "6", "--ignore-eos", "--dtype", "float32", "--json"],
+                       cwd=root, capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+    got = [r["tokens"] for r in json.loads(p.stdout)]
+    eng = engine_for(d, "float32", max_tokens=512, max_batch=2)
+    want = [c.tokens for c in eng.generate([[5, 17, 3, 200], [9]], temp=0, max_tokens=6, ignore_eos=True)]
+    assert got == want
