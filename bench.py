@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--model 1b|3b|8b] [--dtype bfloat16|float32]
                     [--layers L] [--no-points] [--no-prefill] [--impl reference]
-    python bench.py --compare zirivik|salulorn|pirozen [--sizes s,m] [--steps K] [--warmup W] [--batch 8]
+    python bench.py --compare zirivik|salulorn|pirozen|saluzen [--sizes s,m] [--steps K] [--warmup W] [--batch 8]
 
 Default run: the layer sizes of Llama 3.2 1B with random weights, bfloat16, a batch of 8 sequences with random
 prompts of unequal lengths 128..1024, context 4096.  ``--model 3b``: prompts 64..2048, context 4096; ``--model 8b``:
@@ -17,7 +17,8 @@ made of.  Every step reads gigabytes of weights, far more than the 126 MB L2, so
 
 ``--compare zirivik`` (or ``salulorn``, ``pirozen``) leaves all of that alone and prints another line: prefill (one step of
 2,048 tokens) and decode (graph-replayed steps of a batch) of models of that design whose layers have the sizes of real models,
-beside Llama models of the same width, depth, heads and feed-forward size (Pirozen: beside Zirivik models of windowed attention
+beside Llama models of the same width, depth, heads and feed-forward size (Saluzen: beside Salulorn models, the engine's other
+mix of recurrent, windowed and latent layers; Pirozen: beside Zirivik models of windowed attention
 layers with experts of the same sizes, the closest the engine has), with the device time of every launcher of one prefill step
 and of decode steps run eagerly (``profile``), so that like kernels can be set side by side.
 """
@@ -195,9 +196,31 @@ def zirivik_attention_config(width, heads, kv_heads, head_dim, ff, vocab, window
             "logit_softcap": 30.0, "layers": [{"type": "attention", "mixer": att, "mlp": moe} for _ in range(4 * blocks)]}
 
 
-DESIGNS = {"zirivik": zirivik_config, "salulorn": salulorn_config, "pirozen": pirozen_config}
+def saluzen_config(width, heads, kv_heads, head_dim, ff, vocab, window, expert_ff, blocks=2):
+    """Layers of a real model's sizes in the design's own mix: latent attention, latent attention on the layer before's
+    latents, causal attention beside a state-space mixer (heads of 64 with states of 128 rows, four taps), attention in chunks
+    beside the gated delta rule (heads of 128 x 128, four taps), each with a dense feed-forward; `blocks` times."""
+    del expert_ff
+    lat = {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": head_dim, "kv_rank": 512, "q_rank": width * 3 // 4, "scale": 128 ** -0.5,
+           "rot": {"base": 10000.0, "dims": 64}}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5}
+    causal = dict(left, rot={"base": 500000.0, "dims": head_dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+    chunked = dict(left, rot={"base": 1000000.0, "dims": head_dim // 2}, mask={"size": window})
+    ssm = {"heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    delta = {"heads": width // 128, "kv_heads": max(1, width // 256), "dim": 128, "vdim": 128, "conv": 4}
+    dense = {"kind": "dense", "ff": ff}
+    layers = []
+    for _ in range(blocks):
+        at = len(layers)
+        layers += [{"type": "latent_attention", "mixer": lat, "mlp": dense}, {"type": "latent_attention", "mixer": dict(lat, kv_from=at), "mlp": dense},
+                   {"type": "parallel", "mixer": {"left": causal, "right": ssm}, "mlp": dense},
+                   {"type": "parallel_2", "mixer": {"left": chunked, "right": delta, "left_scale": 0.8, "right_scale": 0.5}, "mlp": dense}]
+    return {"architecture": "Saluzen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers}
+
+
+DESIGNS = {"zirivik": zirivik_config, "salulorn": salulorn_config, "pirozen": pirozen_config, "saluzen": saluzen_config}
 #: the model a design stands beside, where that is not Llama
-COUNTERPARTS = {"pirozen": ("zirivik", zirivik_attention_config)}
+COUNTERPARTS = {"pirozen": ("zirivik", zirivik_attention_config), "saluzen": ("salulorn", salulorn_config)}
 
 #: name -> (width, heads, kv_heads, head_dim, ff, vocab, window, expert_ff)
 COMPARE_SIZES = {"s": (2048, 32, 8, 64, 8192, 32768, 1024, 2048), "m": (4096, 32, 8, 128, 14336, 32768, 2048, 4096)}
@@ -285,6 +308,11 @@ def compare_designs(args):
                                   "loop": "all layers, once", "beside": "Zirivik: windowed attention + 8 experts of ff %d, 2 a row" % eff})
         elif design == "zirivik":
             row["config"].update({"experts": "8 of ff %d, 2 a row" % eff, "retention": "%d heads of 128 x 128" % (width // 128)})
+        elif design == "saluzen":
+            row["config"].update({"latent": "rank 512 + 64 rotated, queries through %d, every second layer on the layer before's latents" % (width * 3 // 4),
+                                  "state_space": "%d heads of 64 with 128 state rows, 4 taps" % (width // 64),
+                                  "delta_rule": "%d heads of 128 x 128 on %d key heads, 4 taps" % (width // 128, max(1, width // 256)),
+                                  "chunk": window, "beside": "Salulorn: gla, windowed attention, gla, latent attention"})
         else:
             row["config"].update({"gla": "%d heads of 64 x 128" % (width // 128), "latent": "rank 512 + 64 rotated, queries through %d" % (width * 3 // 4),
                                   "convolution": "4 taps", "loop": "all layers, once"})

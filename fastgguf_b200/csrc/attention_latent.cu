@@ -337,7 +337,7 @@ latent_expand_kernel(const float *__restrict__ q, int ldq, const float *__restri
                      int ldkp, const bf16 *__restrict__ vp, int ldvp, const float *__restrict__ cos_t, const float *__restrict__ sin_t,
                      int tbl_half, const int *__restrict__ positions, const int *__restrict__ row_seq, const int *__restrict__ table,
                      int width, bf16 *__restrict__ qx, bf16 *__restrict__ Kx, bf16 *__restrict__ Vx, int H, int D, int DR, int DV,
-                     int page_size) {
+                     int page_size, int key_rotated) {
     __shared__ float krot[128];
     pdl_launch_dependents();
     pdl_wait();
@@ -346,8 +346,8 @@ latent_expand_kernel(const float *__restrict__ q, int ldq, const float *__restri
     const float *cs = cos_t + (size_t)pos * tbl_half, *sn = sin_t + (size_t)pos * tbl_half;
     for (int i = threadIdx.x; i < DR / 2; i += blockDim.x) {
         const float a = kv[(size_t)m * ldkv + rot_at + 2 * i], b = kv[(size_t)m * ldkv + rot_at + 2 * i + 1];
-        krot[2 * i] = a * cs[i] - b * sn[i];
-        krot[2 * i + 1] = b * cs[i] + a * sn[i];
+        krot[2 * i] = key_rotated ? a : a * cs[i] - b * sn[i];          // (key_rotated: the part comes from a cache, rotated already)
+        krot[2 * i + 1] = key_rotated ? b : b * cs[i] + a * sn[i];
     }
     __syncthreads();
     const size_t slot = (size_t)table[(size_t)row_seq[m] * width + pos / page_size];
@@ -462,14 +462,48 @@ extern "C" int fg_seq_page_table(const int *cu_rows, int n_seq, int width, int p
     return fg_launch(seq_page_table_kernel, dim3(1), dim3(256), 0, stream, cu_rows, n_seq, width, page_size, table);
 }
 
-extern "C" int fg_latent_expand(const float *q, int ldq, const float *kv, int ldkv, int rot_at, const void *kp, int ldkp, const void *vp,
+extern "C" int fg_latent_expand_ext(const float *q, int ldq, const float *kv, int ldkv, int rot_at, const void *kp, int ldkp, const void *vp,
                                 int ldvp, const float *cos_t, const float *sin_t, int tbl_half, const int *positions, const int *row_seq,
                                 const int *table, int width, void *qx, void *Kx, void *Vx, int M, int H, int D, int DR, int DV,
-                                int page_size, cudaStream_t stream) {
+                                int page_size, int key_rotated, cudaStream_t stream) {
     if (M <= 0) return 0;
     if (H <= 0 || D <= 0 || DR <= 0 || DR % 2 || DR > 128 || DV <= 0 || DV > D + DR || DR / 2 > tbl_half) return FG_ERR_BAD_SIZE;
     return fg_launch(latent_expand_kernel, dim3(M), dim3(256), 0, stream, q, ldq, kv, ldkv, rot_at, (const bf16 *)kp, ldkp, (const bf16 *)vp, ldvp,
-                     cos_t, sin_t, tbl_half, positions, row_seq, table, width, (bf16 *)qx, (bf16 *)Kx, (bf16 *)Vx, H, D, DR, DV, page_size);
+                     cos_t, sin_t, tbl_half, positions, row_seq, table, width, (bf16 *)qx, (bf16 *)Kx, (bf16 *)Vx, H, D, DR, DV, page_size, key_rotated);
+}
+
+extern "C" int fg_latent_expand(const float *q, int ldq, const float *kv, int ldkv, int rot_at, const void *kp, int ldkp, const void *vp, int ldvp,
+                                const float *cos_t, const float *sin_t, int tbl_half, const int *positions, const int *row_seq,
+                                const int *table, int width, void *qx, void *Kx, void *Vx, int M, int H, int D, int DR, int DV,
+                                int page_size, cudaStream_t stream) {
+    return fg_latent_expand_ext(q, ldq, kv, ldkv, rot_at, kp, ldkp, vp, ldvp, cos_t, sin_t, tbl_half, positions, row_seq, table, width, qx, Kx, Vx, M,
+                                H, D, DR, DV, page_size, 0, stream);
+}
+
+// A row's latent and rotated key part out of a cache of latents (one "head" a position: the rotated part in k_pool, the
+// latent in v_pool): c_out [M, R] in the cache's dtype, kr_out [M, DR] float32.  For a layer that reads another layer's cache.
+template <typename T>
+__global__ void latent_fetch_kernel(const T *__restrict__ k_pool, const T *__restrict__ v_pool, const int *__restrict__ positions,
+                                    const int *__restrict__ row_seq, const int *__restrict__ table, int width, int page_size,
+                                    T *__restrict__ c_out, int ldc, float *__restrict__ kr_out, int ldk, int R, int DR) {
+    pdl_wait();
+    const int m = blockIdx.x, pos = positions[m];
+    const size_t at = (size_t)table[(size_t)row_seq[m] * width + pos / page_size] * page_size + pos % page_size;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) c_out[(size_t)m * ldc + i] = v_pool[at * R + i];
+    for (int i = threadIdx.x; i < DR; i += blockDim.x) kr_out[(size_t)m * ldk + i] = to_f32<T>(k_pool[at * DR + i]);
+}
+
+extern "C" int fg_latent_fetch(const void *k_pool, const void *v_pool, int dtype, const int *positions, const int *row_seq, const int *table,
+                               int width, int page_size, void *c_out, int ldc, float *kr_out, int ldk, int M, int R, int DR, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (R <= 0 || DR <= 0) return FG_ERR_BAD_SIZE;
+    if (dtype == FG_F32)
+        return fg_launch(latent_fetch_kernel<float>, dim3(M), dim3(128), 0, stream, (const float *)k_pool, (const float *)v_pool, positions,
+                                  row_seq, table, width, page_size, (float *)c_out, ldc, kr_out, ldk, R, DR);
+    if (dtype == FG_BF16)
+        return fg_launch(latent_fetch_kernel<bf16>, dim3(M), dim3(128), 0, stream, (const bf16 *)k_pool, (const bf16 *)v_pool, positions,
+                                  row_seq, table, width, page_size, (bf16 *)c_out, ldc, kr_out, ldk, R, DR);
+    return FG_ERR_BAD_DTYPE;
 }
 
 extern "C" int fg_gate_slice(const void *x, int ldx, int stride, const float *gate, int ldg, void *out, int ldo, int dtype, int M, int H,

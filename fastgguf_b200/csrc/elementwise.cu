@@ -393,7 +393,7 @@ extern "C" int fg_pair_combine(const float *a, const float *b, const float *w_a,
     if (M <= 0) return 0;
     if (E <= 0) return FG_ERR_BAD_SIZE;
     const int threads = E >= 2048 ? 256 : 128;
-    return fg_launch_in_order(pair_combine_kernel, dim3(M), dim3(threads), 0, stream, a, b, w_a, w_b, scale_a, scale_b, eps, out, E, accumulate);
+    return fg_launch(pair_combine_kernel, dim3(M), dim3(threads), 0, stream, a, b, w_a, w_b, scale_a, scale_b, eps, out, E, accumulate);
 }
 
 // ------------------------------------------------------------------ activations in place

@@ -164,6 +164,14 @@ int fg_latent_expand(const float *q, int ldq, const float *kv, int ldkv, int rot
                      int ldvp, const float *cos_t, const float *sin_t, int tbl_half, const int *positions, const int *row_seq,
                      const int *table, int width, void *qx, void *Kx, void *Vx, int M, int H, int D, int DR, int DV,
                      int page_size, cudaStream_t stream);
+/* the same for a key part that is rotated already (key_rotated != 0), and a row's latent (c_out, the cache's dtype) and rotated
+   key part (kr_out, float32) out of a cache of latents, for a layer that reads another layer's cache */
+int fg_latent_expand_ext(const float *q, int ldq, const float *kv, int ldkv, int rot_at, const void *kp, int ldkp, const void *vp,
+                         int ldvp, const float *cos_t, const float *sin_t, int tbl_half, const int *positions, const int *row_seq,
+                         const int *table, int width, void *qx, void *Kx, void *Vx, int M, int H, int D, int DR, int DV,
+                         int page_size, int key_rotated, cudaStream_t stream);
+int fg_latent_fetch(const void *k_pool, const void *v_pool, int dtype, const int *positions, const int *row_seq, const int *table,
+                    int width, int page_size, void *c_out, int ldc, float *kr_out, int ldk, int M, int R, int DR, cudaStream_t stream);
 int fg_gate_slice(const void *x, int ldx, int stride, const float *gate, int ldg, void *out, int ldo, int dtype, int M, int H,
                   int DV, cudaStream_t stream);
 int fg_moe_logits(const void *x, int ldx, const void *W, int ldw, int dtype, float *z, int M, int X, int E, cudaStream_t stream);

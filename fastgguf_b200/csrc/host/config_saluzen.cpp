@@ -7,7 +7,8 @@
 //   attention (a left side) {"heads", "kv_heads", "dim", "vdim", "scale", "rot": {"base", "dims", "scaling": {"factor", "low", "high",
 //                            "original"}}, "mask": {"size"}} - rot, rot.scaling and mask are each left out by a model that has none
 //   latent_attention mixer  {"heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank", "scale", "rot": {"base", "dims"}, "kv_from": j}
-//                           - with kv_from the layer has no key/value latent of its own and reads layer j's
+//                           - with kv_from the layer has no key/value latent of its own and reads layer j's (rot may carry the
+//                           same scaling as a left side's; the two layers' rotations must then agree in it too)
 // Every size and constant above comes from the file.  What the design itself fixes is written here once: a layer is
 // x += norm_b(f(norm_a(x))) around the mixer and around the feed-forward, norms multiply by their weight as stored; the dense
 // feed-forward is SwiGLU; both left sides have biases on q, k, v and rotate the first rot.dims numbers of a head in halves
@@ -160,7 +161,7 @@ public:
                 if (y.rot_dim <= 0 || y.rot_dim % 2 || y.kv_rank <= 0 || y.q_rank <= 0)
                     fail(FG_E_CONFIG, wm + ": rot_dim (even), kv_rank and q_rank must be positive");
                 y.scale = take_float(m, "scale", 1.0 / std::sqrt((double)(y.dim + y.rot_dim)), wm.c_str());
-                y.rot = read_rot(m, wm, y.rot_dim, true, false);
+                y.rot = read_rot(m, wm, y.rot_dim, true, true);
                 if (y.rot.dims != y.rot_dim) fail(FG_E_CONFIG, wm + format(".rot: dims (%lld) must equal rot_dim (%lld)", y.rot.dims, y.rot_dim));
                 const Json *from = m.find("kv_from");
                 if (from && !from->is_null()) {
@@ -169,7 +170,8 @@ public:
                     const Layer &o = c.layers[(size_t)y.kv_from];
                     if (o.type != "latent_attention" || o.kv_from >= 0)
                         fail(FG_E_CONFIG, wm + format(": kv_from names layer %lld, which keeps no latent of its own", y.kv_from));
-                    if (o.kv_rank != y.kv_rank || o.rot_dim != y.rot_dim || o.rot.base != y.rot.base)
+                    if (o.kv_rank != y.kv_rank || o.rot_dim != y.rot_dim || o.rot.base != y.rot.base || o.rot.scaled != y.rot.scaled ||
+                        (y.rot.scaled && (o.rot.factor != y.rot.factor || o.rot.low != y.rot.low || o.rot.high != y.rot.high || o.rot.original != y.rot.original)))
                         fail(FG_E_CONFIG, wm + format(": kv_rank, rot_dim and rot of layer %lld must equal this layer's", y.kv_from));
                 }
             } else {

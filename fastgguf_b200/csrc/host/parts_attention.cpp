@@ -313,7 +313,7 @@ public:
         const int HQ = d_ + dr_;
         // A step of whole prompts in bfloat16 whose head sizes the tensor-core kernels take: ordinary multi-head attention over
         // keys and values expanded for the step's tokens (nothing older is in the cache), in pools of the step's own.
-        bool whole_prompts = !shared_kv_ && !b.single_token && !b.host_seq_start.empty() && !rt.plain_kernels && rt.dtype == FG_BF16 && (HQ == 64 || HQ == 128) &&
+        bool whole_prompts = !b.single_token && !b.host_seq_start.empty() && !rt.plain_kernels && rt.dtype == FG_BF16 && (HQ == 64 || HQ == 128) &&
                              dv_ <= HQ && io.page_size == 64 && b.n_seq <= 1024 && k_up_.t.dtype == FG_BF16 && v_up_.t.dtype == FG_BF16;
         for (size_t s = 0; whole_prompts && s < b.host_seq_start.size(); s++) whole_prompts = b.host_seq_start[s] == 0;
         if (whole_prompts) {
@@ -325,7 +325,14 @@ public:
                 width = std::max(width, n);
             }
             Tensor cn = rt.arena->matrix(M, r_, FG_BF16);
-            FG_LAUNCH("mix", fg_rmsnorm_strided, down.ptr<float>() + qr_, (int)down.ld, kvn_w_.t.ptr<float>(), cn.data, cn.dtype, (int)cn.ld, M, r_, eps_, rt.stream);
+            Tensor kr;                               // shared latents: the owner's rotated key parts of the step's rows, out of its cache
+            if (shared_kv_) {
+                kr = rt.arena->matrix(M, dr_, FG_F32);
+                FG_LAUNCH("mix", fg_latent_fetch, io.k_pool, io.v_pool, io.cache_dtype, b.positions, b.row_seq, table, b.table_width, P, cn.data, (int)cn.ld,
+                          kr.ptr<float>(), (int)kr.ld, M, r_, dr_, rt.stream);
+            } else
+                FG_LAUNCH("mix", fg_rmsnorm_strided, down.ptr<float>() + qr_, (int)down.ld, kvn_w_.t.ptr<float>(), cn.data, cn.dtype, (int)cn.ld, M, r_, eps_,
+                          rt.stream);
             Tensor kp = k_lin_.forward(rt, cn, nullptr, Tensor(), FG_BF16, false, nullptr, nullptr);
             Tensor vp = v_lin_.forward(rt, cn, nullptr, Tensor(), FG_BF16, false, nullptr, nullptr);
             int *tmp_table = (int *)rt.arena->alloc((size_t)b.n_seq * width * sizeof(int));
@@ -333,8 +340,9 @@ public:
             Tensor qx = rt.arena->matrix(M, (int64_t)H_ * HQ, FG_BF16), ox = rt.arena->matrix(M, (int64_t)H_ * HQ, FG_BF16);
             void *Kx = rt.arena->alloc(pool_elems * 2), *Vx = rt.arena->alloc(pool_elems * 2);
             FG_LAUNCH("mix", fg_seq_page_table, b.cu_rows, b.n_seq, width, P, tmp_table, rt.stream);
-            FG_LAUNCH("mix", fg_latent_expand, q.ptr<float>(), (int)q.ld, down.ptr<float>(), (int)down.ld, qr_ + r_, kp.data, (int)kp.ld, vp.data, (int)vp.ld,
-                      cos_t, sin_t, dr_ / 2, b.positions, b.row_seq, tmp_table, width, qx.data, Kx, Vx, M, H_, d_, dr_, dv_, P, rt.stream);
+            FG_LAUNCH("mix", fg_latent_expand_ext, q.ptr<float>(), (int)q.ld, shared_kv_ ? kr.ptr<float>() : down.ptr<float>(),
+                      shared_kv_ ? (int)kr.ld : (int)down.ld, shared_kv_ ? 0 : qr_ + r_, kp.data, (int)kp.ld, vp.data, (int)vp.ld, cos_t, sin_t, dr_ / 2,
+                      b.positions, b.row_seq, tmp_table, width, qx.data, Kx, Vx, M, H_, d_, dr_, dv_, P, shared_kv_ ? 1 : 0, rt.stream);
             if (b.max_new >= 64)
                 FG_LAUNCH("attn", fg_attention_prefill_tc_ext, qx.data, (int)qx.ld, ox.data, (int)ox.ld, b.cu_rows, b.seq_start, tmp_table, width, Kx, Vx,
                           n_pages, b.n_seq, b.max_new, H_, H_, HQ, P, scale_, 0, 0, 0.f, sinks, rt.stream);
