@@ -44,19 +44,35 @@
  *                                   checkpoint}   a decay per key channel and token, sigmoid(low-rank(h) + b)^(1/tau); state as
  *                                   retention's; tensors q/k/v/g/o_proj.weight, decay_down/up.weight, decay_up.bias, norm.weight
  *                 "sink_attention" {hidden_size, n_heads, n_kv_heads, head_dim, v_head_dim, scale, window: 0, softcap: 0,
- *                                   conv_taps: 0, bias: false, o_bias: false, sink: false, qk_norm: null | "whole" | "head",
- *                                   gate: null | "head", eps, position: PART | null}
+ *                                   chunk: 0, conv_taps: 0, bias: false, o_bias: false, sink: false, unit_sink: false,
+ *                                   qk_norm: null | "whole" | "head", gate: null | "head" | "full", eps, position: PART | null}
  *                                   grouped-query attention with biases, a short convolution over time (its last inputs are
  *                                   per-sequence state), norms over the whole of q and of k ("whole": weights [heads * head_dim])
  *                                   or per head ("head": one weight [head_dim] for all heads), rotation in the position part's
  *                                   layout (adjacent pairs, or halves of the rotated part), capped scores, a sink, a sigmoid
- *                                   gate per head from the mixer's input ("head": g_proj.weight [heads, hidden]); tensors
+ *                                   gate per head from the mixer's input ("head": g_proj.weight [heads, hidden]) or per number
+ *                                   ("full": [heads * v_head_dim, hidden]); chunk c instead of a window: a row sees the keys of
+ *                                   its run of c positions counted from the sequence's first; unit_sink: a sink of score 0; tensors
  *                                   q/k/v/o_proj.weight, q/k/v_proj.bias, o_proj.bias, q/k/v_conv.weight, q/k_norm.weight,
  *                                   sinks, g_proj.weight
  *                 "latent_attention" {hidden_size, n_heads, head_dim, rot_dim, v_head_dim, kv_rank, q_rank, scale, eps,
- *                                   sink: false, gate: false, position: PART}   keys and values from one latent a token plus a
- *                                   shared rotated key part (only those are cached); tensors q_down/q_up/kv_down/k_up/v_up/
- *                                   o_proj/g_proj.weight, q_down_norm/kv_down_norm.weight, sinks
+ *                                   sink: false, gate: false, shared_kv: false, position: PART}   keys and values from one latent
+ *                                   a token plus a shared rotated key part (only those are cached); shared_kv: no latent of its
+ *                                   own, the schedule entry reads an earlier entry's cache; tensors q_down/q_up/kv_down/k_up/
+ *                                   v_up/o_proj/g_proj.weight, q_down_norm/kv_down_norm.weight, sinks
+ *                 "state_space"    {hidden_size, n_heads, v_head_dim, state_size, n_groups: 1, conv_taps: 1, norm_groups: 1, eps}
+ *                                   in_proj = [z | x | B | C | dt], convolution + SiLU over x, B, C, S_t = exp(-exp(A_log) dt)
+ *                                   S_(t-1) + dt B x^T, y = S^T C + D x, y silu(z) normalised in norm_groups parts; state
+ *                                   (convolution inputs and S) float32 per sequence; tensors in_proj/o_proj.weight, conv.weight,
+ *                                   conv.bias, dt_bias, A_log, D, norm.weight
+ *                 "gated_delta"    {hidden_size, n_heads, n_kv_heads, head_dim, v_head_dim, conv_taps: 1, eps, unit_eps: 1e-6,
+ *                                   q_scale: null = 1/sqrt(head_dim)}   convolved q, k, v, unit q and k, S <- g S; u = beta (v -
+ *                                   S^T k); S <- S + k u^T; o = S^T q, a norm per head and a SiLU gate; tensors q/k/v/b/a/g/
+ *                                   o_proj.weight, q/k/v_conv.weight, A_log, dt_bias, norm.weight
+ *                 "mixer_pair"     {hidden_size, left: {kind, params}, right: {kind, params}, left_scale: 1, right_scale: 1,
+ *                                   normalize: false, eps}   two mixers on the same rows, y = left_scale f(left) + right_scale
+ *                                   f(right), f an RMS norm over the width with a weight where normalize is true; tensors
+ *                                   left.<the left mixer's>, right.<the right mixer's>, left_norm.weight, right_norm.weight
  *   feed_forward  "swiglu"         {hidden_size, d_ff}
  *                 "mlp"            {hidden_size, d_ff, activation: "relu2"}   down(act(up x))
  *                 "moe"            {hidden_size, d_ff, n_experts, top_k, limit, alpha: 1.702, router: "sigmoid_input"}
