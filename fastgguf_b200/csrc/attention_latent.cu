@@ -316,7 +316,7 @@ __global__ void latent_merge_kernel(const float *__restrict__ part, T *__restric
 // table[s][i] = first page of sequence s in the step's own pools + i, for i < pages of s; sequences one after another
 __global__ void seq_page_table_kernel(const int *__restrict__ cu_rows, int n_seq, int width, int page_size, int *__restrict__ table) {
     __shared__ int base[1025];
-    pdl_launch_dependents();
+    // (only steps of whole prompts run this kernel, between two tensor-memory kernels: its successor is released when it ends)
     pdl_wait();
     if (threadIdx.x == 0) {
         int at = 0;
@@ -339,7 +339,7 @@ latent_expand_kernel(const float *__restrict__ q, int ldq, const float *__restri
                      int width, bf16 *__restrict__ qx, bf16 *__restrict__ Kx, bf16 *__restrict__ Vx, int H, int D, int DR, int DV,
                      int page_size, int key_rotated) {
     __shared__ float krot[128];
-    pdl_launch_dependents();
+    pdl_launch_dependents_small_step(gridDim.x);
     pdl_wait();
     const int m = blockIdx.x, HQ = D + DR;
     const int pos = positions[m];

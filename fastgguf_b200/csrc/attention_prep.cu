@@ -27,7 +27,7 @@ qkv_prepare_kernel(const float *__restrict__ proj, int ld, const float *__restri
                    int rot_halves) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
-    pdl_launch_dependents();
+    pdl_launch_dependents_small_step(gridDim.x);
     pdl_wait();
     const int m = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
     const int Cq = H * hd, Ck = KV * hd, C = Cq + Ck + KV * hdv;
@@ -131,7 +131,7 @@ latent_append_kernel(const float *__restrict__ kv, int ld, const float *__restri
                      const int *__restrict__ block_table, int table_width, T *__restrict__ k_pool, T *__restrict__ v_pool, int rank,
                      int rot_dim, int page_size) {
     __shared__ float scratch[32];
-    pdl_launch_dependents();
+    pdl_launch_dependents_small_step(gridDim.x);
     pdl_wait();
     const int m = blockIdx.x, tid = threadIdx.x;
     const int pos = positions[m];
@@ -176,7 +176,7 @@ template <typename T>
 __global__ void __launch_bounds__(PREP_THREADS)
 rmsnorm_strided_kernel(const float *__restrict__ x, int ldx, const float *__restrict__ w, T *__restrict__ out, int ldo, int E, float eps) {
     __shared__ float scratch[32];
-    pdl_launch_dependents();
+    pdl_launch_dependents_small_step(gridDim.x);
     pdl_wait();
     const float *src = x + (size_t)blockIdx.x * ldx;
     float ss = 0.f;

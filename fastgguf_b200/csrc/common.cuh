@@ -113,6 +113,15 @@ __device__ __forceinline__ bool elect_one() {
 // FASTGGUF_PDL=0 turns the attribute off; the two instructions are then no-ops.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// For kernels of a block a row that stand between two contractions.  In a step of at most 64 rows the contractions are the
+// weight-streaming kernel, and the row-wise kernel releases its successor at once, so that the next contraction fetches its
+// first weights meanwhile.  In a larger step they are the persistent tensor-memory kernels: a short kernel that released its
+// successor at its start and then sat resident, waiting, let the second contraction start beside the first, and now and then
+// a prompt step never finished (a hardware wait: every wait of these kernels' own is bounded).  There the successor is
+// released when the row-wise kernel ends.
+__device__ __forceinline__ void pdl_launch_dependents_small_step(unsigned rows) {
+    if (rows <= 64) pdl_launch_dependents();
+}
 
 #include <cstdlib>
 // Function attributes (the dynamic shared memory limit) belong to a kernel on ONE device: a launcher sets them the

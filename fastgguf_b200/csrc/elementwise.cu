@@ -301,7 +301,7 @@ __global__ void norm_add_norm_kernel(const float *__restrict__ t, const float *_
                                      float eps_next) {
     __shared__ float scratch[32];
     extern __shared__ __align__(16) float row[];        // [E] the updated residual row, when a next norm is wanted
-    pdl_launch_dependents();
+    pdl_launch_dependents_small_step(gridDim.x);
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * E;
     float ss = 0.f;

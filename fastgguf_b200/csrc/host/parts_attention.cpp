@@ -339,6 +339,10 @@ public:
             const size_t pool_elems = (size_t)n_pages * H_ * P * HQ;
             Tensor qx = rt.arena->matrix(M, (int64_t)H_ * HQ, FG_BF16), ox = rt.arena->matrix(M, (int64_t)H_ * HQ, FG_BF16);
             void *Kx = rt.arena->alloc(pool_elems * 2), *Vx = rt.arena->alloc(pool_elems * 2);
+            // a sequence's last page is filled only as far as the sequence goes, and the attention kernel reads whole pages: what lies
+            // behind must be numbers (a masked key has weight zero, but zero times whatever the arena held before need not be zero)
+            FG_CUDA(cudaMemsetAsync(Kx, 0, pool_elems * 2, rt.stream));
+            FG_CUDA(cudaMemsetAsync(Vx, 0, pool_elems * 2, rt.stream));
             FG_LAUNCH("mix", fg_seq_page_table, b.cu_rows, b.n_seq, width, P, tmp_table, rt.stream);
             FG_LAUNCH("mix", fg_latent_expand_ext, q.ptr<float>(), (int)q.ld, shared_kv_ ? kr.ptr<float>() : down.ptr<float>(),
                       shared_kv_ ? (int)kr.ld : (int)down.ld, shared_kv_ ? 0 : qr_ + r_, kp.data, (int)kp.ld, vp.data, (int)vp.ld, cos_t, sin_t, dr_ / 2,

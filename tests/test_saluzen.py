@@ -470,6 +470,42 @@ def test_a_far_token_is_remembered(tmp_path):
         assert np.abs(last[0] - last[1]).max() > 1e-4 * np.abs(last[0]).max(), (name, np.abs(last[0] - last[1]).max() / np.abs(last[0]).max())
 
 
+def test_many_steps_back_to_back():
+    """A hundred and fifty prompt steps of drawn shapes - one to three sequences of 2 to 2,048 tokens, every third step a prompt
+    of 2,048 - each followed by three decode steps, at sizes where every contraction and attention runs on the tensor cores and
+    the row-wise kernels between them are short against them: every step ends with finite logits (prompts that end inside a
+    page leave the rest of the page to whatever the memory held before), and a repeated prompt gives the same logits."""
+    from fastgguf_b200.engine.api import Engine
+    from fastgguf_b200.registry import config_from_dict
+    left = dict(heads=16, kv_heads=4, dim=64, vdim=64, scale=0.125)
+    cfg = config(1024, 4096, [
+        (latent(16, 64, 64, 64, 256, 768, 0.09, 10000.0), dense(4096)),
+        (latent(16, 64, 64, 64, 256, 768, 0.09, 10000.0, kv_from=0), dense(4096)),
+        (parallel(attn(**left, rot=(500000.0, 32), scaling=(8.0, 1.0, 4.0, 8192)), ssm(16, 64, 128, 1, 4, 1)), dense(4096)),
+        (parallel_2(attn(**left, rot=(1000000.0, 32), size=512), delta(8, 4, 128, 128, 4), 0.8, 0.5), dense(4096)),
+    ], eps=1e-6)
+    eng = Engine.from_random(config_from_dict(cfg), 3, dtype="bfloat16", max_tokens=8192, max_batch=4, max_seq_len=4096)
+    rng = np.random.default_rng(5)
+    fixed = tokens_for(cfg, 2048, 90)
+    first = None
+    for i in range(150):
+        n_seq = int(rng.integers(1, 4))
+        lens = [2048] if i % 3 == 0 else [int(rng.integers(2, 2049)) for _ in range(n_seq)]
+        slots = [eng.acquire() for _ in lens]
+        toks = [fixed if n == 2048 and i % 3 == 0 else tokens_for(cfg, n, 1000 + 7 * i + k) for k, n in enumerate(lens)]
+        got = eng.step_host([entry(s, t, [len(t) - 1]) for s, t in zip(slots, toks)])
+        assert np.isfinite(got).all()
+        if i % 3 == 0:
+            first = got if first is None else first
+            assert np.array_equal(got, first)
+        for _ in range(3):
+            assert np.isfinite(eng.step_host([entry(s, [int(rng.integers(0, 4096))]) for s in slots])).all()
+        for s in slots:
+            eng.release(s)
+    eng.check_device()
+    eng.cache.check()
+
+
 # ------------------------------------------------------------------------------ generation through the entry point
 @pytest.mark.parametrize("use_graphs", [False, True])
 @pytest.mark.parametrize("which", ["a", "b"])
