@@ -260,10 +260,12 @@ def compare_designs(args):
                 t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 engine.check_device()
                 t0.record(stream)
-                engine.step_host([StepEntry(slot, toks, [PREFILL_TOKENS - 1])])
+                logits = engine.step_host([StepEntry(slot, toks, [PREFILL_TOKENS - 1])])
                 t1.record(stream)
                 t1.synchronize()
                 engine.release(slot)
+                if not np.isfinite(logits).all():
+                    raise RuntimeError(f"{label}: the prompt step's logits are not all numbers")
                 return t0.elapsed_time(t1)
             times = [prefill_once() for _ in range(3 + 5)][3:]
             pms = sorted(times)[len(times) // 2]
