@@ -241,6 +241,7 @@ gated_group_norm_kernel(const float *__restrict__ y, int ldy, const float *__res
     const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float *yr = y + (size_t)m * ldy, *gr = g + (size_t)m * ldg;
     TO *orow = out + (size_t)m * ldo;
+    const bool whole = w_period >= C, by_group = w_period == group;
     if (group >= 1024) {
         // few wide groups: the whole block takes a group (fixed reduction order: lanes, then warps in order)
         for (int b0 = blockIdx.y * group; b0 < C; b0 += gridDim.y * group) {
@@ -253,7 +254,8 @@ gated_group_norm_kernel(const float *__restrict__ y, int ldy, const float *__res
             for (int i = threadIdx.x; i < group; i += 256) {
                 const int c = b0 + i;
                 const float sg = rec_silu(gr[c]);
-                orow[c] = from_f32<TO>(gate_first ? yr[c] * sg * inv * w[c % w_period] : yr[c] * inv * w[c % w_period] * sg);
+                const float wc = w[whole ? c : (by_group ? i : c % w_period)];        // (no division where the weight spans the row or a group)
+                orow[c] = from_f32<TO>(gate_first ? yr[c] * sg * inv * wc : yr[c] * inv * wc * sg);
             }
         }
         return;
@@ -270,7 +272,8 @@ gated_group_norm_kernel(const float *__restrict__ y, int ldy, const float *__res
         for (int i = lane; i < group; i += 32) {
             const int c = b0 + i;
             const float sg = rec_silu(gr[c]);
-            orow[c] = from_f32<TO>(gate_first ? yr[c] * sg * inv * w[c % w_period] : yr[c] * inv * w[c % w_period] * sg);
+            const float wc = w[whole ? c : (by_group ? i : c % w_period)];        // (no division where the weight spans the row or a group)
+                orow[c] = from_f32<TO>(gate_first ? yr[c] * sg * inv * wc : yr[c] * inv * wc * sg);
         }
     }
 }
