@@ -214,7 +214,7 @@ def saluzen_config(width, heads, kv_heads, head_dim, ff, vocab, window, expert_f
         at = len(layers)
         layers += [{"type": "latent_attention", "mixer": lat, "mlp": dense}, {"type": "latent_attention", "mixer": dict(lat, kv_from=at), "mlp": dense},
                    {"type": "parallel", "mixer": {"left": causal, "right": ssm}, "mlp": dense},
-                   {"type": "parallel_2", "mixer": {"left": chunked, "right": delta, "left_scale": 0.8, "right_scale": 0.5}, "mlp": dense}]
+                   {"type": "parallel_2", "mixer": {"left": chunked, "right": delta, "left_scale": 0.7, "right_scale": 0.6}, "mlp": dense}]
     return {"architecture": "Saluzen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers}
 
 

@@ -80,7 +80,7 @@ CASE_B = config(128, 300, [
 
 # head sizes of 64 and 128 (the tensor-core kernels in bfloat16), states of 128 and 64 rows, a chunk past a page
 CASE_C = config(256, 333, [
-    (parallel(attn(4, 1, 64, 64, 0.1, rot=(250000.0, 64), scaling=(4.0, 1.0, 4.0, 128)), ssm(2, 64, 128, 1, 4, 2)), dense(128)),
+    (parallel(attn(4, 1, 64, 64, 0.1, rot=(300000.0, 64), scaling=(5.0, 1.0, 3.0, 128)), ssm(2, 64, 128, 1, 4, 2)), dense(128)),
     (latent(4, 64, 64, 128, 64, 64, 0.09, 10000.0), None),
     (parallel_2(attn(2, 1, 128, 128, 0.09, rot=(1000.0, 32), size=70), delta(2, 1, 128, 64, 3), 0.8, 0.6), dense(192)),
     (latent(2, 64, 64, 64, 64, 32, 0.1, 10000.0, kv_from=1), dense(64)),

@@ -133,10 +133,10 @@ MIXERS = {
     "delta rule, one key head, one tap, value size that does not fill a warp": (parallel_2(A_SMALL, delta(6, 1, 8, 12, 1), 0.0, 0.5), "right"),
     "delta rule, keys of 48, four taps": (parallel_2(A_SMALL, delta(2, 2, 48, 16, 4), 0.0, 1.0), "right"),
     "both sides of a normalised pair": (parallel(attn(4, 2, 24, 40, 0.3, rot=(100.0, 12)), ssm(3, 24, 16, 1, 4, 1)), None),
-    "both sides of a weighted pair": (parallel_2(attn(6, 3, 16, 8, 0.4, size=5), delta(4, 2, 16, 24, 2), 0.8, 0.5), None),
+    "both sides of a weighted pair": (parallel_2(attn(6, 3, 16, 8, 0.4, size=5), delta(4, 2, 16, 24, 2), 0.9, 0.6), None),
     "latent attention, small": (latent(3, 16, 8, 24, 40, 48, 0.2, 10000.0), None),
     "latent attention, one head": (latent(1, 8, 16, 8, 12, 20, 0.3, 500.0), None),
-    "long attention, unit sink, head 64": (parallel(attn(4, 2, 64, 64, 0.125, rot=(250000.0, 64), scaling=(4.0, 1.0, 4.0, 128)), S_SMALL), "left"),
+    "long attention, unit sink, head 64": (parallel(attn(4, 2, 64, 64, 0.125, rot=(300000.0, 64), scaling=(5.0, 1.0, 3.0, 128)), S_SMALL), "left"),
     "long attention, chunks past a page, head 128, five query heads a key head": (parallel_2(attn(5, 1, 128, 128, 0.09, rot=(1000.0, 32), size=70), D_SMALL, 1.0, 0.0), "left"),
     "long attention, chunks of a page, keys 128 and values 64": (parallel_2(attn(2, 1, 128, 64, 0.09, size=64), D_SMALL, 1.0, 0.0), "left"),
     "long state space, state 128, head 64": (parallel(A_SMALL, ssm(2, 64, 128, 1, 4, 2)), "right"),
@@ -246,7 +246,7 @@ def test_sinks_take_weight_from_the_keys(tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("size", [7, 64, 65, 96])
+@pytest.mark.parametrize("size", [7, 64, 65, 100])
 def test_one_key_at_a_chunks_edge(tmp_path, size, dtype):
     """Weights and inputs made so that ONE key far outweighs all others for every later query: the key projection is the
     query projection with its input columns shifted, the special row is the later rows' common direction shifted back.
@@ -482,7 +482,7 @@ def test_many_steps_back_to_back():
         (latent(16, 64, 64, 64, 256, 768, 0.09, 10000.0), dense(4096)),
         (latent(16, 64, 64, 64, 256, 768, 0.09, 10000.0, kv_from=0), dense(4096)),
         (parallel(attn(**left, rot=(500000.0, 32), scaling=(8.0, 1.0, 4.0, 8192)), ssm(16, 64, 128, 1, 4, 1)), dense(4096)),
-        (parallel_2(attn(**left, rot=(1000000.0, 32), size=512), delta(8, 4, 128, 128, 4), 0.8, 0.5), dense(4096)),
+        (parallel_2(attn(**left, rot=(1000000.0, 32), size=512), delta(8, 4, 128, 128, 4), 0.9, 0.4), dense(4096)),
     ], eps=1e-6)
     eng = Engine.from_random(config_from_dict(cfg), 3, dtype="bfloat16", max_tokens=8192, max_batch=4, max_seq_len=4096)
     rng = np.random.default_rng(5)
